@@ -6,12 +6,19 @@ from .qwen2 import Qwen2Config, build_qwen2_spec, read_config_json
 from .registry import (Architecture, register_architecture, registered_architectures, resolve,
                        spec_from_config_dict, unregister_architecture)
 from .shapes import named_shape, shape_names
+from .zodosun import ARCHITECTURE as ZODOSUN_ARCHITECTURE
+from .zodosun import MODEL_TYPE as ZODOSUN_MODEL_TYPE
+from .zodosun import ZodosunConfig, build_zodosun_spec
 
 register_architecture(
     Architecture(QWEN2_ARCHITECTURE, QWEN2_MODEL_TYPE, Qwen2Config, build_qwen2_spec), replace=True)
 
+register_architecture(
+    Architecture(ZODOSUN_ARCHITECTURE, ZODOSUN_MODEL_TYPE, ZodosunConfig, build_zodosun_spec), replace=True)
+
 __all__ = [
     "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "ScheduleEntry",
+    "ZodosunConfig", "build_zodosun_spec",
     "build_qwen2_spec", "named_shape", "read_config_json", "register_architecture",
     "registered_architectures", "resolve", "shape_names", "spec_from_config_dict", "unregister_architecture",
 ]

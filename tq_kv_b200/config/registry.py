@@ -2,8 +2,8 @@
 
 An entry holds the typed configuration class that reads the architecture's
 config.json and the builder that turns a configuration into a `ModelSpec`.
-`resolve()` picks the entry from config.json's `architectures[0]` (or, failing
-that, from `model_type`).  Adding an architecture = one `register_architecture`
+`resolve()` picks the entry from config.json's `architectures[0]` (or its
+`architecture`, or, failing both, from `model_type`).  Adding an architecture = one `register_architecture`
 call; nothing else in the package names an architecture.
 
 Reference: the engine has no dispatch by class name (src/engine.rs:234 ignores
@@ -46,6 +46,9 @@ def registered_architectures() -> list[str]:
 def resolve(config_dict: dict) -> Architecture:
     """The registry entry for a config.json (given as a dict)."""
     names = config_dict.get("architectures")
+    single = config_dict.get("architecture")            # some architectures name themselves with this key
+    if not (isinstance(names, list) and names) and isinstance(single, str) and single:
+        names = [single]
     if isinstance(names, list) and names:
         name = names[0]
         if name in _ARCHITECTURES:
@@ -57,7 +60,7 @@ def resolve(config_dict: dict) -> Architecture:
         if mt is not None and arch.model_type == mt:
             return arch
     raise ConfigError(
-        "config.json: neither 'architectures' nor a known 'model_type' is given "
+        "config.json: neither 'architectures', 'architecture' nor a known 'model_type' is given "
         f"(registered: {registered_architectures()})")
 
 

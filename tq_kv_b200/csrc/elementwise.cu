@@ -450,3 +450,193 @@ TQ_API int tq_select_tokens(int* tokens, const int* src, const int* sampled, int
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, select_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens,
                          src, sampled, n);
 }
+
+// ---------------------------------------------------------------------------
+// Embedding with sinusoidal positions: out[t, c] = float(table[tokens[t], c]) +
+// (c even ? sin : cos)(pos[t] * rate[c / 2]), the angle and its sine in float32.
+// `rate` holds width/2 (rounded up) float32 frequencies, made by the caller.
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_sinusoid_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                                      const TW* __restrict__ table, const float* __restrict__ rate,
+                                      float* __restrict__ out, int H, int V, int* status) {
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
+    const int id = tokens[t];
+    const float p = (float)positions[t];
+    float* o = out + (size_t)t * H;
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && status) atomicOr(status, 1);
+    const TW* row = table + (size_t)(ok ? id : 0) * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float ang = p * rate[c >> 1];
+        const float e = ok ? to_f32<TW>(row[c]) : 0.f;
+        o[c] = e + ((c & 1) ? cosf(ang) : sinf(ang));
+    }
+}
+
+TQ_API int tq_embed_sinusoid(const int* tokens, const int* positions, const void* table, int table_dtype,
+                             const float* rate, float* out, int n_tokens, int H, int V, int* status,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!positions || !rate) return (int)cudaErrorInvalidValue;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == TQ_F32)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_sinusoid_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream,
+                             tokens, positions, (const float*)table, rate, out, H, V, status);
+    if (table_dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_sinusoid_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream,
+                             tokens, positions, (const bf16*)table, rate, out, H, V, status);
+    return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm in groups, optionally gated: a row of `groups * gw` float32 values is
+// cut into consecutive groups of gw; group g becomes
+//   x / sqrt(mean_g(x^2) + eps) * w  [* sigmoid(gate)]
+// with w over the whole row and gate (float32 logits, row stride ldg) entry by
+// entry.  One group is the plain norm; heads * head_width is a norm per head.
+// x and out have row strides of their own, so that x may be a slice of a wider
+// buffer.  `rows` (optional) selects the input rows.  grid (row, group).
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                     const float* __restrict__ gate, int ldg, TO* __restrict__ out, int ldo,
+                                     const int* __restrict__ rows, int gw, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, g = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
+    const int src = rows ? rows[r] : r;
+    const float* xr = x + (size_t)src * ldx + (size_t)g * gw;
+    const float* wr = w + (size_t)g * gw;
+    const float* gr = gate ? gate + (size_t)src * ldg + (size_t)g * gw : nullptr;
+    TO* o = out + (size_t)r * ldo + (size_t)g * gw;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / (float)gw + eps);
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+        float y = (xr[i] / rms) * wr[i];
+        if (gr) y *= 1.f / (1.f + expf(-gr[i]));
+        o[i] = from_f32<TO>(y);
+    }
+}
+
+TQ_API int tq_group_rmsnorm(const float* x, int ldx, const float* w, const float* gate, int ldg, void* out,
+                            int out_dtype, int ldo, const int* rows, int n_rows, int width, int groups, float eps,
+                            cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (groups <= 0 || groups > 65535 || width <= 0 || width % groups) return (int)cudaErrorInvalidValue;
+    const int gw = width / groups;
+    const int threads = gw >= 2048 ? 512 : (gw >= 512 ? 256 : (gw > 64 ? 128 : 64));
+    const dim3 grid(n_rows, groups);
+    if (out_dtype == TQ_F32)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, group_rmsnorm_kernel<float>, grid, dim3(threads), 0, stream, x, ldx, w,
+                             gate, ldg, (float*)out, ldo, rows, gw, eps);
+    if (out_dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, group_rmsnorm_kernel<bf16>, grid, dim3(threads), 0, stream, x, ldx, w,
+                             gate, ldg, (bf16*)out, ldo, rows, gw, eps);
+    return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// acc[t, :] += scale * sum_s  x_s[t, :] / sqrt(mean(x_s[t]^2) + eps) * w_s   for up to four sources:
+// the results of mixers that run side by side, each normed over the whole row with a weight of its own,
+// summed into the float32 residual stream.  One block per row.
+// ---------------------------------------------------------------------------
+struct NormedSources {
+    const float* x[4];
+    const float* w[4];
+    int n;
+};
+
+__global__ void add_normed_kernel(float* __restrict__ acc, NormedSources s, int W, float eps, float scale) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch();
+    float inv[4];
+    for (int k = 0; k < s.n; ++k) {
+        const float* xr = s.x[k] + (size_t)t * W;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+        ss = block_sum(ss, red);
+        inv[k] = 1.f / sqrtf(ss / (float)W + eps);
+    }
+    float* a = acc + (size_t)t * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float y = 0.f;
+        for (int k = 0; k < s.n; ++k) y += (s.x[k][(size_t)t * W + i] * inv[k]) * s.w[k][i];
+        a[i] += scale * y;
+    }
+}
+
+TQ_API int tq_add_normed(float* acc, const float* x0, const float* w0, const float* x1, const float* w1,
+                         const float* x2, const float* w2, const float* x3, const float* w3, int n_sources,
+                         int n_rows, int W, float eps, float scale, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_sources < 1 || n_sources > 4 || W <= 0) return (int)cudaErrorInvalidValue;
+    NormedSources s{{x0, x1, x2, x3}, {w0, w1, w2, w3}, n_sources};
+    for (int k = 0; k < n_sources; ++k)
+        if (!s.x[k] || !s.w[k]) return (int)cudaErrorInvalidValue;
+    const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, add_normed_kernel, dim3(n_rows), dim3(threads), 0, stream, acc, s, W, eps,
+                         scale);
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = tanh(x[t, i]) for a slice of n columns of float32 rows (row strides ldx / ldo).
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void tanh_rows_kernel(const float* __restrict__ x, int ldx, TO* __restrict__ out, int ldo, int n,
+                                 size_t total) {
+    pdl_wait();
+    pdl_launch();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / n;
+        const int i = (int)(idx - t * n);
+        out[t * ldo + i] = from_f32<TO>(tanhf(x[t * ldx + i]));
+    }
+}
+
+TQ_API int tq_tanh_rows(const float* x, int ldx, void* out, int out_dtype, int ldo, int n_rows, int n,
+                        cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * n;
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > (size_t)tq_sm_count() * 16) blocks = (size_t)tq_sm_count() * 16;
+    if (out_dtype == TQ_F32)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, tanh_rows_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, x,
+                             ldx, (float*)out, ldo, n, total);
+    if (out_dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, tanh_rows_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, x,
+                             ldx, (bf16*)out, ldo, n, total);
+    return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// x[i] *= s for float32 x (logits that a model scales by a constant).
+// ---------------------------------------------------------------------------
+__global__ void scale_inplace_kernel(float* __restrict__ x, size_t total, float s) {
+    pdl_wait();
+    pdl_launch();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] *= s;
+}
+
+TQ_API int tq_scale_inplace(float* x, size_t total, float s, cudaStream_t stream) {
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > (size_t)tq_sm_count() * 16) blocks = (size_t)tq_sm_count() * 16;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, scale_inplace_kernel, dim3((int)blocks), dim3(threads), 0, stream, x, total,
+                         s);
+}

@@ -16,6 +16,7 @@ from .. import kernels
 from ..cache import KVLayerView, KVRequest, SequenceCache, StateRequest
 from ..config import ConfigError, ModelSpec
 from ..parts import Runtime, StepBatch, StepContext, WeightSpec, make_block, make_part
+from ..parts.base import shapes_agree
 
 
 class DecoderModel:
@@ -57,7 +58,7 @@ class DecoderModel:
         for part in self._all_parts():
             for ws in part.weight_specs():
                 old = specs.get(ws.name)
-                if old is not None and tuple(old.shape) != tuple(ws.shape):
+                if old is not None and not shapes_agree(old.shape, ws.shape):
                     raise ConfigError(f"tensor '{ws.name}' is wanted with shapes {old.shape} and {ws.shape}")
                 specs.setdefault(ws.name, ws)
         return specs
@@ -105,7 +106,10 @@ class DecoderModel:
         """Runs the step's tokens through the scheduled blocks; returns float32
         logits [wanted rows, vocab] (None if no row is wanted)."""
         rt = self.runtime
-        h = self.embedding.forward(batch.tokens)
+        if getattr(self.embedding, "wants_positions", False):
+            h = self.embedding.forward(batch.tokens, batch.tok_pos)
+        else:
+            h = self.embedding.forward(batch.tokens)
         kernels.mark("embed")
         for i, e in enumerate(self.spec.schedule):
             owner = i if e.cache_of is None else e.cache_of

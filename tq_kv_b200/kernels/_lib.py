@@ -175,6 +175,21 @@ _SIGNATURES = {
                             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int,
                             c_void_p, c_void_p],
     "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_embed_sinusoid": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tq_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                         c_float, c_void_p],
+    "tq_add_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_int, c_float, c_float, c_void_p],
+    "tq_scale_inplace": [c_void_p, c_size_t, c_float, c_void_p],
+    "tq_tanh_rows": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_linear_scan": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float,
+                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_rownorm_qkv_store": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_void_p],
+    "tq_sigmoid_attention": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
                   c_void_p, c_void_p],
     "tq_sample_seeded": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, ctypes.c_ulonglong, c_int,

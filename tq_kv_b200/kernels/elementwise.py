@@ -112,3 +112,85 @@ def random_fill(out: torch.Tensor, key: int, std: float, offset: float = 0.0):
     check(core().tq_random_fill(ptr(out), dtype_code(out), out.numel(), int(key) & ((1 << 64) - 1), float(std),
                                 float(offset), stream()), "random_fill")
     return out
+
+
+def embed_sinusoid(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, rate: torch.Tensor,
+                   out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """out[t, c] = float32(table[tokens[t], c]) + (sin if c is even else cos)(positions[t] * rate[c // 2]).
+    tokens, positions int32 [T]; rate float32 [ceil(H / 2)]; out float32 [T, H]."""
+    T = tokens.shape[0]
+    V, H = table.shape
+    if tokens.dtype != torch.int32 or positions.dtype != torch.int32 or positions.shape[0] < T:
+        raise KernelError("embed_sinusoid: tokens and positions must be int32 [T]")
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, H):
+        raise KernelError("embed_sinusoid: out must be float32 [T, H]")
+    if rate.dtype != torch.float32 or rate.shape[0] < (H + 1) // 2:
+        raise KernelError("embed_sinusoid: rate must be float32 [ceil(H / 2)]")
+    need_contiguous(tokens=tokens, positions=positions, table=table, rate=rate, out=out)
+    check(core().tq_embed_sinusoid(ptr(tokens), ptr(positions), ptr(table), dtype_code(table), ptr(rate), ptr(out), T, H,
+                                   V, ptr(status), stream()), "embed_sinusoid")
+    return out
+
+
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *, groups: int = 1,
+                  gate: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None):
+    """RMS norm in `groups` consecutive groups of a row, times `weight`, optionally times sigmoid(gate) entry by
+    entry.  x float32 [*, W] and gate float32 [*, W] may be column slices of wider buffers (row strides are
+    passed on); weight float32 [W]; out float32 or bfloat16 [R, W]."""
+    W = x.shape[-1]
+    R = out.shape[0]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.shape[0] != W or out.shape[-1] != W:
+        raise KernelError("group_rmsnorm: x and weight must be float32 with matching width")
+    if groups < 1 or W % groups:
+        raise KernelError(f"group_rmsnorm: a width of {W} cannot be cut into {groups} equal groups")
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or (gate is not None and (gate.stride(-1) != 1 or gate.dtype != torch.float32
+                                                                        or gate.shape != x.shape)):
+        raise KernelError("group_rmsnorm: x, gate and out must be contiguous along the row; gate float32 of x's shape")
+    if rows is None and x.shape[0] != R:
+        raise KernelError("group_rmsnorm: out must have as many rows as x when no rows are selected")
+    if rows is not None and (rows.dtype != torch.int32 or rows.shape[0] != R):
+        raise KernelError("group_rmsnorm: rows must be int32 [R]")
+    need_contiguous(weight=weight, rows=rows)
+    check(core().tq_group_rmsnorm(ptr(x), x.stride(0), ptr(weight), ptr(gate), 0 if gate is None else gate.stride(0),
+                                  ptr(out), dtype_code(out), out.stride(0), ptr(rows), R, W, groups, float(eps),
+                                  stream()), "group_rmsnorm")
+    return out
+
+
+def add_normed(acc: torch.Tensor, sources, eps: float, scale: float):
+    """acc[t] += scale * sum over (x, w) in sources of x[t] / sqrt(mean(x[t]^2) + eps) * w.  acc and every x
+    float32 [T, W] contiguous, every w float32 [W]; up to four sources."""
+    T, W = acc.shape
+    sources = list(sources)
+    if not 1 <= len(sources) <= 4:
+        raise KernelError("add_normed: one to four sources")
+    flat = []
+    for x, w in sources:
+        if x.dtype != torch.float32 or w.dtype != torch.float32 or tuple(x.shape) != (T, W) or w.shape[0] != W:
+            raise KernelError("add_normed: sources must be float32 [T, W] with float32 weights [W]")
+        need_contiguous(x=x, w=w)
+        flat += [ptr(x), ptr(w)]
+    flat += [None] * (8 - len(flat))
+    if acc.dtype != torch.float32:
+        raise KernelError("add_normed: acc must be float32")
+    need_contiguous(acc=acc)
+    check(core().tq_add_normed(ptr(acc), *flat, len(sources), T, W, float(eps), float(scale), stream()), "add_normed")
+    return acc
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor):
+    """out = tanh(x) for float32 x [T, n] (may be a column slice: its row stride is passed on)."""
+    T, n = x.shape
+    if x.dtype != torch.float32 or tuple(out.shape) != (T, n) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("tanh_rows: x float32 [T, n], out [T, n], both contiguous along the row")
+    check(core().tq_tanh_rows(ptr(x), x.stride(0), ptr(out), dtype_code(out), out.stride(0), T, n, stream()), "tanh_rows")
+    return out
+
+
+def scale_inplace(x: torch.Tensor, s: float):
+    """x *= s for a contiguous float32 tensor."""
+    if x.dtype != torch.float32:
+        raise KernelError("scale_inplace: x must be float32")
+    need_contiguous(x=x)
+    check(core().tq_scale_inplace(ptr(x), x.numel(), float(s), stream()), "scale_inplace")
+    return x

@@ -3,13 +3,22 @@ from .attention import GQAttention
 from .base import (FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, StepBatch, StepContext, WeightSpec,
                    float32_vector)
 from .block import PrenormResidualBlock
+from .decayed_state import DecayedStateMixer
+from .delta_rule import DeltaRuleMixer
 from .embedding import LMHead, TokenEmbedding
 from .feed_forward import SwiGLU
-from .norm import RMSNorm
+from .norm import GroupRMSNorm, RMSNorm
 from .position import RotaryHalved
+from .side_by_side import SideBySideMixer
+from .sigmoid_attention import SigmoidAttention
 from .registry import make_block, make_part, part_kinds, register_block, register_part, unregister_part
 
 register_part("rms_norm", RMSNorm, replace=True)
+register_part("group_rms_norm", GroupRMSNorm, replace=True)
+register_part("delta_rule_mixer", DeltaRuleMixer, replace=True)
+register_part("decayed_state_mixer", DecayedStateMixer, replace=True)
+register_part("sigmoid_attention", SigmoidAttention, replace=True)
+register_part("side_by_side", SideBySideMixer, replace=True)
 register_part("rotary_halved", RotaryHalved, replace=True)
 register_part("gqa_attention", GQAttention, replace=True)
 register_part("swiglu", SwiGLU, replace=True)
@@ -17,7 +26,8 @@ register_part("token_embedding", TokenEmbedding, replace=True)
 register_part("lm_head", LMHead, replace=True)
 register_block("prenorm_residual", PrenormResidualBlock, replace=True)
 
-__all__ = ["FeedForward", "GQAttention", "LMHead", "Mixer", "Norm", "Part", "PositionEncoding",
+__all__ = ["DecayedStateMixer", "DeltaRuleMixer", "GroupRMSNorm", "SideBySideMixer", "SigmoidAttention",
+           "FeedForward", "GQAttention", "LMHead", "Mixer", "Norm", "Part", "PositionEncoding",
            "PrenormResidualBlock", "RMSNorm", "RotaryHalved", "Runtime", "StepBatch", "StepContext", "SwiGLU",
            "TokenEmbedding", "WeightSpec", "float32_vector", "make_block", "make_part", "part_kinds",
            "register_block", "register_part", "unregister_part"]

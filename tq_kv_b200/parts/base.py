@@ -31,7 +31,9 @@ class WeightSpec:
     """A tensor a part expects.  `role` picks the random-init rule and says
     how the tensor is used: 'matrix' and 'embedding' are operands of matrix
     products and keep their stored precision; 'bias' and 'norm_scale' are
-    widened to float32 when bound."""
+    widened to float32 when bound.  A size of -1 in `shape` is one that only
+    the checkpoint knows (any size is accepted there; random weights need it
+    given)."""
     name: str
     shape: tuple[int, ...]
     role: str
@@ -168,6 +170,12 @@ class PositionEncoding(Part):
                          n_kv_heads: int, head_dim: int, q_out: torch.Tensor, k_out: Optional[torch.Tensor],
                          v_out: Optional[torch.Tensor]) -> None:
         raise NotImplementedError
+
+
+def shapes_agree(want, got) -> bool:
+    """Whether a tensor of shape `got` fits the expected shape `want` (-1 fits any size)."""
+    want, got = tuple(want), tuple(got)
+    return len(want) == len(got) and all(w == g or w == -1 or g == -1 for w, g in zip(want, got))
 
 
 def float32_vector(t: torch.Tensor) -> torch.Tensor:

@@ -22,17 +22,22 @@ class PrenormResidualBlock:
         self.spec = spec
         self.mixer_norm = make_part(spec.part("mixer_norm"))
         self.mixer = make_part(spec.part("mixer"))
-        self.feed_forward_norm = make_part(spec.part("feed_forward_norm"))
-        self.feed_forward = make_part(spec.part("feed_forward"))
+        # a layer may name no feed-forward: it then has the mixer's sublayer only
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = make_part(spec.part("feed_forward_norm"))
+            self.feed_forward = make_part(spec.part("feed_forward"))
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
 
     def forward(self, h, ctx: StepContext) -> None:
         act = ctx.runtime.act_dtype
         x = self._normed(self.mixer_norm, self.mixer, h, act)
         kernels.mark("norms")
         self.mixer.forward(x, ctx, h)
+        if self.feed_forward is None:
+            return
         x = self._normed(self.feed_forward_norm, self.feed_forward, h, act)
         kernels.mark("norms")
         self.feed_forward.forward(x, ctx, h)
@@ -41,6 +46,6 @@ class PrenormResidualBlock:
     def _normed(norm, consumer, h, act):
         """The norm's result for `consumer` — left pending if the consumer only hands it to `kernels.linear`
         (it says so with `takes_pending_norm`) and the norm can be deferred, so that the product may fold it in."""
-        if getattr(consumer, "takes_pending_norm", False) and hasattr(norm, "pending"):
+        if getattr(consumer, "takes_pending_norm", False) and getattr(norm, "pending", None) is not None:
             return norm.pending(h, act)
         return norm.forward(h, act)

@@ -18,10 +18,11 @@ class SwiGLU(FeedForward):
         self.hidden = int(self.params["hidden_size"])
         self.inter = int(self.params["intermediate_size"])
         self.names = dict(self.params.get("names", {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}))
+        self.suffix = self.params.get("weight_suffix", ".weight")     # what follows a projection's name in a tensor's
         self.w_gate_up = self.w_down = None
 
     def _n(self, which):
-        return f"{self.prefix}{self.names[which]}.weight"
+        return f"{self.prefix}{self.names[which]}{self.suffix}"
 
     def weight_specs(self):
         return [WeightSpec(self._n("gate"), (self.inter, self.hidden), "matrix"),

@@ -7,6 +7,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
+from ..config import ConfigError
 from .base import Norm, Runtime, WeightSpec, float32_vector
 
 
@@ -17,13 +18,14 @@ class RMSNorm(Norm):
         super().__init__(spec)
         self.width = int(self.params["width"])
         self.eps = float(self.params["eps"])
+        self.weight_name = self.params.get("weight_name") or self.prefix + "weight"
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self):
-        return [WeightSpec(self.prefix + "weight", (self.width,), "norm_scale")]
+        return [WeightSpec(self.weight_name, (self.width,), "norm_scale")]
 
     def bind(self, tensors, runtime: Runtime, shared=None):
-        self.weight = float32_vector(tensors[self.prefix + "weight"])
+        self.weight = float32_vector(tensors[self.weight_name])
 
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
@@ -35,3 +37,21 @@ class RMSNorm(Norm):
         feeds it to `kernels.linear` lets the product fold the norm in where
         it can (else the norm runs then, as a kernel of its own)."""
         return kernels.PendingNorm(x, self.weight, self.eps, out_dtype)
+
+
+class GroupRMSNorm(RMSNorm):
+    """RMS norm in groups: the row is cut into `groups` equal consecutive
+    parts, each divided by its own sqrt(mean(part^2) + eps); then the whole row
+    times the weight.  One group is the plain norm."""
+    pending = None                      # the products fold in the plain norm only
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.groups = int(self.params.get("groups", 1))
+        if self.groups < 1 or self.width % self.groups:
+            raise ConfigError(f"a norm over {self.width} values cannot be cut into {self.groups} equal groups")
+
+    def forward(self, x, out_dtype, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
+        return kernels.group_rmsnorm(x, self.weight, self.eps, out, groups=self.groups, rows=rows)

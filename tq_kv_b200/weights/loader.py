@@ -48,6 +48,12 @@ def target_dtype(stored: torch.dtype, mode: torch.dtype) -> torch.dtype:
     return torch.bfloat16
 
 
+def _fits(got, want) -> bool:
+    """A stored shape fits an expected one if they agree in every size the model knows (-1: the file says)."""
+    got, want = tuple(got), tuple(want)
+    return len(got) == len(want) and all(w == -1 or w == g for g, w in zip(got, want))
+
+
 def load_tensors(folder: str, expected: dict[str, tuple[int, ...]], ignored: Iterable[str], *, mode: torch.dtype,
                  device) -> dict[str, torch.Tensor]:
     """The expected tensors of `folder` on `device`.  `expected` maps tensor
@@ -58,7 +64,7 @@ def load_tensors(folder: str, expected: dict[str, tuple[int, ...]], ignored: Ite
         missing = sorted(n for n in expected if n not in where)
         unexpected = sorted(n for n in where if n not in expected and n not in ignored)
         wrong = [(n, where[n].entries[n].shape, tuple(shape)) for n, shape in sorted(expected.items())
-                 if n in where and tuple(where[n].entries[n].shape) != tuple(shape)]
+                 if n in where and not _fits(where[n].entries[n].shape, shape)]
         if missing or unexpected or wrong:
             raise WeightsError(folder, missing, unexpected, wrong)
         out: dict[str, torch.Tensor] = {}

@@ -120,6 +120,9 @@ def random_tensor(name: str, shape: tuple[int, ...], role: str, seed: int, dtype
     (the same values on any device)."""
     if role not in _STD:
         raise ValueError(f"no random-init rule for role '{role}' (tensor {name})")
+    if any(int(d) < 0 for d in shape):
+        raise ValueError(f"tensor {name} has a size that only a checkpoint gives ({list(shape)}); "
+                         "random weights need it in the configuration")
     key, std, offset = tensor_key(seed, name), _STD[role], _OFFSET.get(role, 0.0)
     n = 1
     for d in shape:
@@ -153,8 +156,9 @@ def write_model_folder(config_dict: dict, folder: str, seed: int, *, device="cpu
     dtype = storage_dtype(config_dict.get("torch_dtype", "bfloat16"))
     os.makedirs(folder, exist_ok=True)
     full = cfg.to_dict() if hasattr(cfg, "to_dict") else dict(config_dict)
-    full["architectures"] = [arch.name]          # the name the registry resolved, not the config class's own
-    full["model_type"] = arch.model_type
+    if full.get("architecture") != arch.name:    # (a configuration that names itself this way needs no more)
+        full["architectures"] = [arch.name]      # the name the registry resolved, not the config class's own
+        full["model_type"] = arch.model_type
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(full, f, indent=1)
     write_safetensors(os.path.join(folder, "model.safetensors"),
