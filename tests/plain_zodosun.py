@@ -206,3 +206,35 @@ def read_folder(folder: str):
         a, b = meta["data_offsets"]
         out[name] = torch.frombuffer(bytearray(data[a:b]), dtype=dt).reshape(meta["shape"]).clone()
     return cfg, out
+
+
+def write_folder(folder: str, cfg: dict, weights: dict) -> str:
+    """config.json and model.safetensors (bfloat16 / float32 / int32 tensors)."""
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+    names = {torch.bfloat16: "BF16", torch.float32: "F32", torch.int32: "I32", torch.float16: "F16"}
+    header, blobs, at = {}, [], 0
+    for name, t in weights.items():
+        t = t.contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 else \
+            t.view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for b in blobs:
+            f.write(b)
+    return folder
+
+
+def greedy(cfg: dict, weights: dict, prompt: list[int], n: int, dtype=torch.float64) -> list[int]:
+    """n greedy tokens after `prompt`, every step a whole forward pass (ties go to the lowest id)."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(decoder(cfg, weights, toks, dtype)[-1])))
+    return toks[len(prompt):]
