@@ -15,8 +15,9 @@ from zodosun_cases import CASES, folder, oracle_logits, tokens
 pytestmark = pytest.mark.gpu
 ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
 # The recurrences pass rounding on from token to token and the attention's weights are not normalised: the
-# bounds are a few times the largest errors seen (float32 2e-6, bfloat16 2e-2 of the largest logit).
-TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+# bounds are the package's float32 bound and about twice the largest bfloat16 error seen (5.6e-6 and 1.8e-2 of
+# the largest logit).
+TOL = {"float32": 3e-5, "bfloat16": 4e-2}
 
 
 @pytest.fixture(scope="module")
@@ -144,9 +145,9 @@ def test_greedy_generation_through_the_entry_point_and_the_command_line(tmp_root
     assert [r.tokens for r in res] == want and all(r.finish_reason == "length" for r in res)
     assert eng.cache.free_slots == 2
     env = dict(os.environ, PYTHONPATH=ROOT)
-    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "tq"), "run", "--model-path", path, "--dtype", "float32",
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "tq"), "run", path, "--dtype", "float32",
                         "--prompt-ids", ",".join(map(str, prompts[1])), "-n", "10", "--temperature", "0",
-                        "--max-context", "128"], capture_output=True, text=True, env=env, timeout=600)
+                        "--repeat-penalty", "1.0", "--max-context", "128"], capture_output=True, text=True, env=env, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [int(t) for t in p.stdout.strip().splitlines()[-1].split(",")] == want[1]
 

@@ -151,13 +151,24 @@ __device__ __forceinline__ uint64_t ft_desc_mn(uint32_t saddr, uint32_t mn_strid
            ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-template <int HD, bool PAGED>
+// What the four warps between the two products do with a tile's scores.  FT_SOFTMAX: the weights are
+// exp(score - reference), summed per row, and the result is divided by the sum at the end.  FT_SIGMOID: the weight
+// of key j for the query at position i is sigmoid(score * scale + bias[h, min(i - j, n_dist - 1)]) with a
+// float32 table per head and distance (none: zero); nothing is normalised, so O is never rescaled and the end
+// multiplies head h's row by sigmoid(gate[token, h]) (none: one).  The weights are made in float32 (2^x and the
+// reciprocal of the special-function unit, a few ulp) and rounded to bfloat16 for the second product, as the
+// softmax's are.
+#define FT_SOFTMAX 0
+#define FT_SIGMOID 1
+
+template <int HD, bool PAGED, int WEIGHTS>
 __global__ void __launch_bounds__(FT_THREADS, 2)
 flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         int ring_pages, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
                         int n_seqs, int window, float scale_log2, bf16* __restrict__ out, int nh, int nkv,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, const float* __restrict__ bias, int n_dist,
+                        const float* __restrict__ gate, int ldg) {
     constexpr int SUBS = HD / 64;                          // 64-column sub-tiles of a Q, K or V tile
     constexpr int Q_BYTES = SUBS * FT_SUB_BYTES;
     constexpr int KV_BYTES = SUBS * FT_KV_SUB_BYTES;       // a K or V tile of 64 keys
@@ -336,12 +347,38 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
             for (int c = 0; c < FT_BN; c += 32) ft_ld32_issue(s_addr + c, sv + c);
             ft_ld_wait();
-            if (!inside) {
+            if (WEIGHTS == FT_SOFTMAX && !inside) {
 #pragma unroll
                 for (int j = 0; j < FT_BN; ++j) {
                     const int key = j0 + j;
                     if (key < j_lo || key > j_hi) sv[j] = -INFINITY;     // a masked key: 2^-inf = 0 below
                 }
+            }
+            if constexpr (WEIGHTS == FT_SIGMOID) {
+                // weight = 1 / (1 + 2^-(score * scale * log2 e + bias * log2 e)); a masked key has weight 0.
+                // Neighbouring rows read neighbouring entries of the head's table (distance = row - key).
+                const float* hb = bias ? bias + (size_t)h * n_dist : nullptr;
+                float packed[FT_BN / 2];
+#pragma unroll
+                for (int j = 0; j < FT_BN; j += 2) {
+                    float w2[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int key = j0 + j + u;
+                        float x = sv[j + u] * scale_log2;
+                        if (hb) x = fmaf(hb[min(max(p_row - key, 0), n_dist - 1)], 1.4426950408889634f, x);
+                        float r;
+                        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(1.f + ft_exp2(-x)));
+                        w2[u] = (inside || key <= j_hi) ? r : 0.f;
+                    }
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(w2[0], w2[1]);
+                    packed[j >> 1] = __uint_as_float(*reinterpret_cast<uint32_t*>(&pk));
+                }
+                ft_st32(s_addr, packed);
+                if (it > 0 && !ft_wait(ft_smem(p_full), (it - 1) & 1, true)) { *failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                ft_arrive(ft_smem(p_full));
+                continue;
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four chains instead of one of 64
 #pragma unroll
@@ -402,7 +439,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok && !ft_wait(ft_smem(o_done), 0, true)) { *failed = 1; ok = false; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (ok) {
-            const float inv = 1.f / l_run;
+            float inv = 1.f / l_run;
+            if constexpr (WEIGHTS == FT_SIGMOID)
+                inv = gate ? 1.f / (1.f + expf(-gate[(size_t)(tok0 + min(i_row, len - 1)) * ldg + h])) : 1.f;
             bf16* orow = out + ((size_t)(tok0 + min(i_row, len - 1)) * nh + h) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
@@ -443,23 +482,24 @@ static int ft_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-template <int HD, bool PAGED>
+template <int HD, bool PAGED, int WEIGHTS = FT_SOFTMAX>
 static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* block_table,
                      int table_width, int ring_pages, const int* cu_seqlens, const int* start_pos, int n_seqs,
                      int n_tokens, int window, float scale, bf16* out, int nh, int nkv, int* status,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const float* bias = nullptr, int n_dist = 0, const float* gate = nullptr,
+                     int ldg = 0) {
     constexpr int SMEM = (HD / 64) * (FT_SUB_BYTES + 4 * FT_KV_SUB_BYTES) + 256;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, PAGED>,
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<HD, PAGED, WEIGHTS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const dim3 grid(nh, (n_tokens + FT_BM - 1) / FT_BM + n_seqs);
-    return tq_launch_pdl(TQ_PDL_PREFILL_ATTENTION, flash_prefill_tc_kernel<HD, PAGED>, grid, dim3(FT_THREADS), SMEM, stream,
-                         mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
-                         scale * 1.4426950408889634f, out, nh, nkv, status);
+    return tq_launch_pdl(TQ_PDL_PREFILL_ATTENTION, flash_prefill_tc_kernel<HD, PAGED, WEIGHTS>, grid, dim3(FT_THREADS), SMEM,
+                         stream, mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, n_seqs, window,
+                         scale * 1.4426950408889634f, out, nh, nkv, status, bias, n_dist, gate, ldg);
 }
 
 // q, out [T, nh * hd] bfloat16.  Keys/values: packed [T, nkv * hd] (every
@@ -489,6 +529,41 @@ TQ_API int tq_flash_prefill_tc(const void* q, const void* k_packed, const void* 
     if (st) return st;
 #define TQ_FT(H, P) return ft_launch<H, P>(mq, mk, mv, block_table, table_width, ring_pages, cu_seqlens, start_pos, \
                                            n_seqs, n_tokens, window, scale, (bf16*)out, nh, nkv, status, stream)
+    if (hd == 128 && paged) TQ_FT(128, true);
+    if (hd == 128 && !paged) TQ_FT(128, false);
+    if (hd == 64 && paged) TQ_FT(64, true);
+    TQ_FT(64, false);
+#undef TQ_FT
+}
+
+
+// The same kernel with sigmoid weights (FT_SIGMOID above): causal, no window, keys and values of one width (64 or
+// 128).  bias: float32 [nh, n_dist] or null; gate: float32 logits, one per token and head (row stride ldg), or null.
+TQ_API int tq_sigmoid_prefill_tc(const void* q, const void* k_packed, const void* v_packed, const void* k_pages,
+                                 const void* v_pages, long long n_pages, const int* block_table, int table_width,
+                                 int page_tokens, const int* cu_seqlens, const int* start_pos, int n_seqs, int n_tokens,
+                                 float scale, const float* bias, int n_dist, const float* gate, int ldg, void* out,
+                                 int nh, int nkv, int hd, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || (hd != 64 && hd != 128)) return (int)cudaErrorNotSupported;
+    if ((long long)(n_tokens + FT_BM - 1) / FT_BM + n_seqs > 65535) return (int)cudaErrorNotSupported;   // grid.y
+    if (bias && n_dist <= 0) return (int)cudaErrorInvalidValue;
+    const bool paged = k_packed == nullptr;
+    if (paged && (page_tokens != 64 || !k_pages || !v_pages || !block_table)) return (int)cudaErrorNotSupported;
+    CUtensorMap mq, mk, mv;
+    int st = ft_map(&mq, q, (uint64_t)n_tokens, (uint64_t)nh * hd, (uint64_t)nh * hd, FT_BM);
+    if (st) return st;
+    if (paged) {
+        st = ft_map(&mk, k_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+        if (!st) st = ft_map(&mv, v_pages, (uint64_t)n_pages * nkv * 64, (uint64_t)hd, (uint64_t)hd, 64);
+    } else {
+        st = ft_map(&mk, k_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+        if (!st) st = ft_map(&mv, v_packed, (uint64_t)n_tokens, (uint64_t)nkv * hd, (uint64_t)nkv * hd, FT_BN);
+    }
+    if (st) return st;
+#define TQ_FT(H, P) return ft_launch<H, P, FT_SIGMOID>(mq, mk, mv, block_table, table_width, 0, cu_seqlens, start_pos, \
+                                                       n_seqs, n_tokens, 0, scale, (bf16*)out, nh, nkv, status, stream, \
+                                                       bias, n_dist, gate, ldg)
     if (hd == 128 && paged) TQ_FT(128, true);
     if (hd == 128 && !paged) TQ_FT(128, false);
     if (hd == 64 && paged) TQ_FT(64, true);

@@ -5,9 +5,11 @@ from typing import Optional
 
 import torch
 
-from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
+from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
 
 MAX_WIDTH = 256
+NOT_SUPPORTED = 801      # cudaErrorNotSupported: the tensor-core kernel declines the shape
+USE_TC_ATTENTION = True  # prompts in bfloat16 with keys and values 64 or 128 wide: the tcgen05 kernel
 
 
 def rownorm_qkv_store(x: torch.Tensor, q_out: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int,
@@ -99,6 +101,19 @@ def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_
         part = scratch
     need_contiguous(q=q, out=out, k_packed=k_packed, v_packed=v_packed, k_pages=k_pages, v_pages=v_pages,
                     block_table=block_table, bias=bias)
+    n_seqs = cu_seqlens.shape[0] - 1
+    if (USE_TC_ATTENTION and q.dtype == torch.bfloat16 and T > n_seqs and key_dim == value_dim
+            and key_dim in (64, 128)):
+        # prompts on the tcgen05 tensor cores: the softmax kernel's pipeline with sigmoid weights
+        # (csrc/flash_prefill_tc.cu)
+        st = core().tq_sigmoid_prefill_tc(
+            ptr(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages),
+            0 if k_pages is None else k_pages.shape[0], ptr(block_table), table_width, page_tokens, ptr(cu_seqlens),
+            ptr(start_pos), n_seqs, T, float(scale), ptr(bias), n_dist, ptr(gate), ldg, ptr(out), n_heads, n_kv_heads,
+            key_dim, ptr(tc_status_word(q.device)), stream())
+        if st != NOT_SUPPORTED:
+            check(st, "sigmoid_prefill_tc")
+            return out
     check(core().tq_sigmoid_attention(
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width,
         page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos), float(scale), ptr(bias), n_dist,
