@@ -172,8 +172,153 @@ def timed_by_class(run, reps: int = 3) -> dict:
     return {k: statistics.median(r.get(k, 0.0) for r in runs) for k in runs[0]}
 
 
+# ---- --design zodosun: the Zodosun decoder beside the Qwen2 decoder of equal size ---------------------------------
+DESIGN_SIZES = {          # width, feed-forward width, layers (delta, delta, side-by-side, delta), vocabulary
+    "1k": (1024, 2816, 4, 32000),
+    "2k": (2048, 5632, 4, 32000),
+    "4k": (4096, 11008, 4, 32000),
+}
+FP32_FMA_PER_SM_PER_CLOCK = 128          # float32 lanes of an SM: the scan's roofline is 2 * this * SMs * clock
+
+
+def design_configs(width: int, ff: int, layers: int, vocab: int) -> tuple[dict, dict]:
+    """A Zodosun configuration with heads of 128 and the Qwen2 configuration of the same width, depth, heads,
+    feed-forward and vocabulary."""
+    heads, kv = width // 128, max(1, width // 512)
+    delta = {"type": "general_delta", "mixer": {"heads": heads, "dim": 128, "rank": 64},
+             "mlp": {"kind": "dense", "ff": ff}}
+    side = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 4096,
+                 "bias_rows": 64, "q_temp": {"coef": 0.1, "every": 256}},
+        "right": {"heads": heads, "dim": 128, "vdim": 128,
+                  "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(1, heads - 1)) for h in range(heads)]}}}
+    zod = {"architecture": "Zodosun", "vocab": vocab, "width": width, "logit_scale": 1.0,
+           "norm": {"eps": 1e-6, "groups": 1}, "max_positions": 8192,
+           "layers": [side if i % 4 == 2 else delta for i in range(layers)]}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16",
+            "num_hidden_layers": layers, "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": kv,
+            "head_dim": 128, "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+            "tie_word_embeddings": False, "use_sliding_window": False, "sliding_window": None,
+            "max_window_layers": layers, "max_position_embeddings": 8192}
+    return zod, qwen
+
+
+def design_compare(args) -> int:
+    """Prefill and decode of the Zodosun decoder and of the Qwen2 decoder of equal size, random weights, bfloat16:
+    device time of a 2,048-token prompt, of decode steps at batch 8 and 64 (replayed graphs), and the time by
+    class of kernel with what each class reaches of its roofline."""
+    import torch
+    import tq_kv_b200 as tq
+    from tq_kv_b200 import kernels
+    from tq_kv_b200.engine import StepRow
+    pk, pk_src = peaks()
+    gen = torch.Generator().manual_seed(0)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    P, ctx = args.prompt, args.prompt + 512
+    out = {"design": "zodosun", "beside": "qwen2", "dtype": "bf16", "data": "synthetic (random weights)",
+           "peaks": {**pk, "source": pk_src}, "prompt": P, "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in args.sizes.split(","):
+            width, ff, layers, vocab = DESIGN_SIZES[name]
+            rec = out["sizes"][name] = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
+            for model, cfg in zip(("zodosun", "qwen2"), design_configs(width, ff, layers, vocab)):
+                eng = tq.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=64, max_context=ctx,
+                                            max_tokens=64 * ctx)
+                r = rec[model] = {}
+
+                def prompt_rows(n_rows):
+                    slots = [eng.new_sequence() for _ in range(n_rows)]
+                    return slots, [StepRow(s, torch.randint(0, vocab, (P,), generator=gen).tolist(), [P - 1]) for s in slots]
+
+                # prefill: one prompt, device time after two warm-up runs
+                times = []
+                for i in range(2 + 5):
+                    slots, rows = prompt_rows(1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    eng.step(rows)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1))
+                    eng.release(slots[0])
+                r["prefill_ms"] = round(statistics.median(times[2:]), 3)
+                r["prefill_tok_s"] = round(P / (r["prefill_ms"] * 1e-3))
+
+                def one_prompt():
+                    slots, rows = prompt_rows(1)
+                    eng.step(rows)
+                    eng.release(slots[0])
+
+                r["prefill_classes_us"] = {k: round(v, 1) for k, v in timed_by_class(one_prompt).items() if k != "start"}
+                # decode: batches of 8 and 64 sequences that hold P tokens, replayed graphs, 64 timed steps
+                for B in (8, 64):
+                    slots = [eng.new_sequence() for _ in range(B)]
+                    for a in range(0, B, 8):
+                        eng.step([StepRow(s, torch.randint(0, vocab, (P,), generator=gen).tolist(), []) for s in slots[a:a + 8]])
+                    toks = torch.randint(0, vocab, (16 + 64, B), generator=gen).tolist()
+                    for i in range(16):
+                        eng.step([StepRow(s, [toks[i][j]], [0]) for j, s in enumerate(slots)], keep_logits=False)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for i in range(16, 80):
+                        eng.step([StepRow(s, [toks[i][j]], [0]) for j, s in enumerate(slots)], keep_logits=False)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    eng.check_status()
+                    ms = e0.elapsed_time(e1) / 64
+                    r[f"decode_b{B}_ms"] = round(ms, 4)
+                    r[f"decode_b{B}_tok_s"] = round(B / (ms * 1e-3))
+                    if B == 64:
+                        eng.use_graphs = False
+
+                        def one_step():
+                            eng.step([StepRow(s, [1], [0]) for s in slots], keep_logits=False)
+
+                        one_step()
+                        r["decode_b64_classes_us"] = {k: round(v, 1) for k, v in timed_by_class(one_step).items()
+                                                      if k != "start"}
+                        eng.use_graphs = True
+                    for s in slots:
+                        eng.release(s)
+                del eng
+                torch.cuda.empty_cache()
+            # what the classes reach of their rooflines
+            heads, d = width // 128, 128
+            z, q = rec["zodosun"], rec["qwen2"]
+            n_delta = sum(1 for i in range(layers) if i % 4 != 2)
+            n_side = layers - n_delta
+            mhz = 1900.0
+            fp32_tflops = 2 * FP32_FMA_PER_SM_PER_CLOCK * sms * mhz * 1e6 / 1e12
+            scan_flops = P * heads * d * d * (8 * n_delta + 5 * n_side)
+            attn_flops = 4 * heads * d * P * (P + 1) / 2
+            roof = rec["roofline"] = {"fp32_fma_tflops_nominal": round(fp32_tflops, 1)}
+            roof["zodosun.prefill.scan.frac_of_fp32_fma"] = round(
+                scan_flops / (z["prefill_classes_us"]["scan"] * 1e-6) / 1e12 / fp32_tflops, 3)
+            roof["zodosun.prefill.attention.frac_of_bf16"] = round(
+                attn_flops * n_side / (z["prefill_classes_us"]["attention"] * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+            roof["qwen2.prefill.attention.frac_of_bf16"] = round(
+                attn_flops * layers / (q["prefill_classes_us"]["attention"] * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+            state_bytes = 64 * heads * d * d * 4 * 2 * layers            # every layer reads and writes a state per head
+            kv_row = 2 * max(1, width // 512) * d * 2
+            roof["zodosun.decode_b64.scan.frac_of_hbm"] = round(
+                state_bytes / (z["decode_b64_classes_us"]["scan"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+            roof["zodosun.decode_b64.attention.frac_of_hbm"] = round(
+                64 * (P + 16) * kv_row * n_side / (z["decode_b64_classes_us"]["attention"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+            roof["qwen2.decode_b64.attention.frac_of_hbm"] = round(
+                64 * (P + 16) * kv_row * layers / (q["decode_b64_classes_us"]["attention"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+    out["clocks"] = clocks.summary()
+    out["gpu_launches"] = kernels.launches[0]
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["zodosun"],
+                    help="instead of the default workload: this design beside the Qwen2 decoder of equal size")
+    ap.add_argument("--sizes", default="1k,2k,4k", help="with --design: which of the sizes 1k, 2k, 4k (the model's width)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
@@ -203,6 +348,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design is not None:
+        return design_compare(args)
     if args.warmup < 3:
         args.warmup = 3
     unequal = args.workload == "unequal"

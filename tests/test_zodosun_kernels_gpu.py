@@ -128,12 +128,14 @@ def test_scan_with_constant_decay(H, d, e):
     for n in lens:
         cu.append(cu[-1] + n)
     out = torch.full((T, H * e), float("nan"), device=DEV)
+    given = proj.clone()
     for silu in (True, False):
         state.copy_(before)
+        proj = given.clone()                                    # the kernels work in place
         kernels.linear_scan(proj, state, _i32(cu), _i32(slots), out, n_seqs=4, heads=H, key_dim=d, value_dim=e,
                             off_q=offs["q"], off_k=offs["k"], off_v=offs["v"],
                             head_decay=torch.tensor(decay, device=DEV), silu=silu)
-        want, st = _scan_reference("decay", proj, offs, H, d, e, [before[s] for s in slots],
+        want, st = _scan_reference("decay", given, offs, H, d, e, [before[s] for s in slots],
                                    list(zip(cu, cu[1:])), decay=decay, silu=silu)
         _close(out, want, 2e-5, f"outputs silu={silu}")
         for s, S in zip(slots, st):
@@ -159,8 +161,8 @@ def test_scan_with_the_delta_rule(H, d):
     for m in lens:
         cu.append(cu[-1] + m)
     out = torch.full((T, n), float("nan"), device=DEV)
-    kernels.linear_scan(proj, state, _i32(cu), _i32(slots), out, n_seqs=4, heads=H, key_dim=d, value_dim=d, off_q=0,
-                        off_k=n, off_v=2 * n, off_a=4 * n, decay_logit=decay_logit)
+    kernels.linear_scan(proj.clone(), state, _i32(cu), _i32(slots), out, n_seqs=4, heads=H, key_dim=d, value_dim=d,
+                        off_q=0, off_k=n, off_v=2 * n, off_a=4 * n, decay_logit=decay_logit.clone())      # (in place)
     want, st = _scan_reference("delta", proj, offs, H, d, d, [before[s] for s in slots], list(zip(cu, cu[1:])),
                                decay_logit=decay_logit)
     _close(out, want, 5e-5, "outputs")
@@ -181,12 +183,13 @@ def test_scan_in_portions_equals_scan_at_once():
         kw = dict(n_seqs=1, heads=H, key_dim=d, value_dim=d, off_q=0, off_k=n, off_v=2 * n)
         kw.update(dict(off_a=4 * n) if mode == "delta" else dict(head_decay=torch.tensor([0.9, 0.99], device=DEV), silu=True))
         whole, s1 = torch.empty(T, n, device=DEV), torch.zeros(3, H, d, d, device=DEV)
-        kernels.linear_scan(proj, s1, _i32([0, T]), _i32([1]), whole,
-                            **kw, **(dict(decay_logit=logit) if mode == "delta" else {}))
+        kernels.linear_scan(proj.clone(), s1, _i32([0, T]), _i32([1]), whole,
+                            **kw, **(dict(decay_logit=logit.clone()) if mode == "delta" else {}))
         parts, s2, at = torch.empty(T, n, device=DEV), torch.zeros(3, H, d, d, device=DEV), 0
         for m in (1, 2, 16, 17, 31, 3):
-            kernels.linear_scan(proj[at:at + m], s2, _i32([0, m]), _i32([2]), parts[at:at + m],
-                                **kw, **(dict(decay_logit=logit[at:at + m]) if mode == "delta" else {}))
+            kernels.linear_scan(proj[at:at + m].clone(), s2, _i32([0, m]), _i32([2]), parts[at:at + m],
+                                single_tokens=m == 1,
+                                **kw, **(dict(decay_logit=logit[at:at + m].clone()) if mode == "delta" else {}))
             at += m
         assert at == T
         _close(parts, whole, 1e-6, mode)
@@ -358,3 +361,30 @@ def test_row_norm_temperature_and_cache_append(dtype):
         page = table[b * 2 + p // 64].item()
         assert torch.equal(kp[page, 0, p % 64], k_out[t]) and torch.equal(vp[page, 0, p % 64], v_out[t])
     assert kp[2].abs().max().item() == 0                 # a page of no sequence
+
+
+@pytest.mark.parametrize("H, d, e", [(2, 24, 24), (1, 64, 64), (1, 128, 128), (1, 200, 200), (3, 8, 48), (1, 100, 20)])
+def test_the_one_token_kernel_equals_the_scan(H, d, e):
+    """Six sequences of one token each through the kernel for decoding and through the general one."""
+    from tq_kv_b200 import kernels
+    torch.manual_seed(e)
+    B, n = 6, H * d
+    slots = _i32([4, 0, 5, 2, 7, 1])
+    cu = _i32(list(range(B + 1)))
+    for mode in (["delta", "decay"] if d == e else ["decay"]):
+        proj = torch.randn(B, 4 * n + H * e + 4, device=DEV)
+        logit = torch.randn(B, n, device=DEV)
+        outs, states = [], []
+        for single in (True, False):
+            state = torch.randn(8, H, d, e, generator=torch.Generator(device=DEV).manual_seed(1), device=DEV)
+            out = torch.empty(B, H * e, device=DEV)
+            kw = dict(n_seqs=B, heads=H, key_dim=d, value_dim=e, off_q=0, off_k=n, off_v=2 * n, single_tokens=single)
+            if mode == "delta":
+                kw.update(off_a=3 * n + H * e, decay_logit=logit.clone())
+            else:
+                kw.update(head_decay=torch.tensor([0.9, 0.5, 0.99][:H], device=DEV), silu=True)
+            kernels.linear_scan(proj.clone(), state, cu, slots, out, **kw)
+            outs.append(out)
+            states.append(state)
+        _close(outs[0], outs[1], 1e-5, mode + " outputs")
+        _close(states[0], states[1], 1e-5, mode + " states")

@@ -182,8 +182,9 @@ _SIGNATURES = {
                       c_int, c_int, c_float, c_float, c_void_p],
     "tq_scale_inplace": [c_void_p, c_size_t, c_float, c_void_p],
     "tq_tanh_rows": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "tq_linear_scan": [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float,
-                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_linear_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                       c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                       c_int, c_void_p],
     "tq_rownorm_qkv_store": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_void_p],

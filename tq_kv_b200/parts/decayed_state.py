@@ -68,7 +68,7 @@ class DecayedStateMixer(Mixer):
         o = torch.empty((T, self.vw), dtype=torch.float32, device=dev)
         kernels.linear_scan(proj, ctx.state, b.cu_seqlens, b.slots, o, n_seqs=b.n_seqs, heads=self.heads,
                             key_dim=self.key_dim, value_dim=self.value_dim, off_q=0, off_k=self.qk, off_v=2 * self.qk,
-                            head_decay=self.decay_t, silu=self.activation == "silu")
+                            head_decay=self.decay_t, silu=self.activation == "silu", single_tokens=b.single_tokens)
         kernels.mark("scan")
         y = torch.empty((T, self.vw), dtype=act, device=dev)
         kernels.group_rmsnorm(o, self.norm_w, self.eps, y, groups=1, gate=proj[:, 2 * self.qk + self.vw:])

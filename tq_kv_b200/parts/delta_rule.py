@@ -98,7 +98,7 @@ class DeltaRuleMixer(Mixer):
         o = torch.empty((T, n), dtype=torch.float32, device=dev)
         kernels.linear_scan(proj, ctx.state, b.cu_seqlens, b.slots, o, n_seqs=b.n_seqs, heads=self.heads,
                             key_dim=self.dim, value_dim=self.dim, off_q=0, off_k=n, off_v=2 * n, off_a=4 * n,
-                            decay_logit=decay_logit, unit_eps=self.unit_eps)
+                            decay_logit=decay_logit, unit_eps=self.unit_eps, single_tokens=b.single_tokens)
         kernels.mark("scan")
         y = torch.empty((T, n), dtype=act, device=dev)
         kernels.group_rmsnorm(o, self.norm_w, self.eps, y, groups=self.heads, gate=proj[:, 3 * n:4 * n])
