@@ -43,14 +43,23 @@ __device__ __forceinline__ uint32_t fd_pack(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// What becomes of a chunk's scores.  FD_SOFTMAX: the online softmax described above.  FD_SIGMOID: the weight of key
+// j for the token at position i and head h is sigmoid(score * scale + bias[h, min(i - j, n_dist - 1)]) (a float32
+// table per head and distance; none: zero), nothing is normalised, so the warps' and the splits' partial outputs
+// simply add; with one split head h's output is multiplied by sigmoid(gate[token, h]) (none: one), with more the
+// kernel that adds the splits does that.
+#define FD_SOFTMAX 0
+#define FD_SIGMOID 1
+
 // FD_CHUNK: keys per warp iteration — 16, or 32 for heads of up to 64 dims, whose 16-key chunks would be too small.
-template <int HD, int FD_CHUNK>
+template <int HD, int FD_CHUNK, int WEIGHTS = FD_SOFTMAX>
 __global__ void __launch_bounds__(FD_WARPS * 32)
 flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     const int* __restrict__ block_table, int table_width, int ring_pages,
                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int window, float scale_log2,
                     bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv,
-                    int n_splits) {
+                    int n_splits, const float* __restrict__ bias = nullptr, int n_dist = 0,
+                    const float* __restrict__ gate = nullptr, int ldg = 0) {
     constexpr int ROW = HD * 2 + 16;                       // bytes per key row in shared memory (padded)
     constexpr int TILE = FD_CHUNK * ROW;                   // one K or V chunk
     constexpr int WARP_BYTES = FD_STAGES * 2 * TILE;
@@ -162,6 +171,22 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 fd_mma(s[n + 1], qf[ks], kb[2], kb[3]);
             }
         }
+        float corr[2] = {1.f, 1.f};
+        if constexpr (WEIGHTS == FD_SIGMOID) {
+            // rows gid and gid + 8 are heads g * n_rep + gid (+ 8); a key past the range weighs nothing
+            const float* b0 = (bias && gid < n_rep) ? bias + (size_t)(g * n_rep + gid) * n_dist : nullptr;
+            const float* b1 = (bias && gid + 8 < n_rep) ? bias + (size_t)(g * n_rep + gid + 8) * n_dist : nullptr;
+#pragma unroll
+            for (int nt = 0; nt < ST; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + nt * 8 + 2 * tid4 + (e & 1);
+                    const float* hb = (e >> 1) ? b1 : b0;
+                    float x = s[nt][e] * scale_log2;
+                    if (hb && j < hi) x = fmaf(hb[min(pos - j, n_dist - 1)], 1.4426950408889634f, x);
+                    s[nt][e] = j < hi ? 1.f / (1.f + exp2f(-x)) : 0.f;
+                }
+        } else {
         // scale, mask keys beyond the range, online softmax (rows gid and gid + 8)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -173,7 +198,6 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 s[nt][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
-        float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -202,6 +226,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int n = 0; n < NT; ++n) {
             o[n][0] *= corr[0]; o[n][1] *= corr[0];
             o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
         }
 #pragma unroll
         for (int kk = 0; kk < FD_CHUNK / 16; ++kk) {
@@ -243,6 +268,22 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         }
     }
     __syncthreads();
+    if constexpr (WEIGHTS == FD_SIGMOID) {
+        for (int e = threadIdx.x; e < n_rep * HD; e += blockDim.x) {
+            const int r = e / HD, d = e - r * HD;
+            float a = 0.f;
+#pragma unroll
+            for (int w = 0; w < FD_WARPS; ++w) a += ms[((size_t)w * 16 + r) * RS + d];
+            const int h = g * n_rep + r;
+            if (n_splits == 1) {
+                const float gt = gate ? 1.f / (1.f + expf(-gate[(size_t)t * ldg + h])) : 1.f;
+                out[((size_t)t * nh + h) * HD + d] = __float2bfloat16_rn(a * gt);
+            } else {
+                part_acc[(((size_t)t * nh + h) * n_splits + split) * HD + d] = a;
+            }
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < n_rep * HD; e += blockDim.x) {
         const int r = e / HD, d = e - r * HD;
         float m = -INFINITY;
@@ -272,11 +313,12 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     }
 }
 
-template <int HD>
+template <int HD, int WEIGHTS = FD_SOFTMAX>
 static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, const int* table, int table_width,
                                int ring_pages, const int* tok_pos, const int* tok_seq, int window, float scale,
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
-                               int pdl_family, cudaStream_t stream) {
+                               int pdl_family, cudaStream_t stream, const float* bias = nullptr, int n_dist = 0,
+                               const float* gate = nullptr, int ldg = 0) {
     constexpr int ROW = HD * 2 + 16;
     constexpr int FD_CHUNK = HD <= 64 ? 32 : 16;
     constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * 2 * FD_CHUNK * ROW;
@@ -287,15 +329,15 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK, WEIGHTS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK>, grid, dim3(FD_WARPS * 32), smem, stream, q, kp, vp, table,
-                         table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out, part_acc,
-                         part_ml, nh, nkv, n_splits);
+    return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK, WEIGHTS>, grid, dim3(FD_WARPS * 32), smem, stream, q,
+                         kp, vp, table, table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out,
+                         part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg);
 }
 
 // Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach
@@ -338,4 +380,32 @@ TQ_API int tq_flash_decode(const void* q, const void* k_pages, const void* v_pag
                            int nkv, int hd, int n_splits, cudaStream_t stream) {
     return flash_decode_launch(q, k_pages, v_pages, block_table, table_width, ring_pages, page_tokens, tok_pos, tok_seq,
                                window, scale, out, part_acc, part_ml, n_tokens, nh, nkv, hd, n_splits, 1, stream);
+}
+
+
+// The same kernel with sigmoid weights (FD_SIGMOID above) for keys and values of one width: out (one split) or the
+// splits' partial outputs in `part` [T, nh, n_splits, hd] float32, which tq_sigmoid_attention's sum kernel adds and
+// gates.  Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach.
+TQ_API int tq_sigmoid_flash_decode(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                   int table_width, int page_tokens, const int* tok_pos, const int* tok_seq, float scale,
+                                   const float* bias, int n_dist, const float* gate, int ldg, void* out, float* part,
+                                   int n_tokens, int nh, int nkv, int hd, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || page_tokens != FD_PAGE || nkv > 65535 || n_splits > 65535)
+        return (int)cudaErrorNotSupported;
+    if (n_splits < 1 || (n_splits > 1 && !part) || (bias && n_dist <= 0)) return (int)cudaErrorInvalidValue;
+#define TQ_FD(H)                                                                                                        \
+    case H:                                                                                                             \
+        return launch_flash_decode<H, FD_SIGMOID>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages,          \
+                                                  block_table, table_width, 0, tok_pos, tok_seq, 0, scale, (bf16*)out, \
+                                                  part, nullptr, n_tokens, nh, nkv, n_splits, TQ_PDL_FLASH_DECODE,      \
+                                                  stream, bias, n_dist, gate, ldg)
+    switch (hd) {
+        TQ_FD(32);
+        TQ_FD(64);
+        TQ_FD(96);
+        TQ_FD(128);
+        default: return (int)cudaErrorNotSupported;
+    }
+#undef TQ_FD
 }

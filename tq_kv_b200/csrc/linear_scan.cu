@@ -334,8 +334,9 @@ static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
                          args);
 }
 
-// Which form: wide tiles (four columns a thread, 256 threads) once they fill the GPU; else one column a thread,
-// in blocks as large as still leave a block for a quarter of the SMs (see the kernel's comment).
+// Which form.  One column a thread while such blocks still find an SM each (a block that shares its SM's
+// shared-memory pipe with another runs at half the pace), in blocks as large as still leave a block for a quarter
+// of the SMs; four columns a thread beyond that.
 template <int MODE, int KG>
 static int pick_form(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     const long long sms = tq_sm_count();
@@ -343,7 +344,7 @@ static int pick_form(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
         const int ct = threads / KG * rc;
         return (long long)n_seqs * a.H * ((a.e + ct - 1) / ct);
     };
-    if (a.e >= 256 / KG * 4 && blocks(256, 4) >= sms) return launch_scan<MODE, KG, 256, 4>(a, n_seqs, stream);
+    if (a.e >= 256 / KG * 4 && blocks(256, 1) > sms) return launch_scan<MODE, KG, 256, 4>(a, n_seqs, stream);
     if (a.e >= 256 / KG && blocks(256, 1) >= sms / 4) return launch_scan<MODE, KG, 256, 1>(a, n_seqs, stream);
     if (a.e >= 128 / KG && blocks(128, 1) >= sms / 4) return launch_scan<MODE, KG, 128, 1>(a, n_seqs, stream);
     if (KG < 32 || a.e >= 2) return launch_scan<MODE, KG, 64, 1>(a, n_seqs, stream);

@@ -277,3 +277,18 @@ TQ_API int tq_sigmoid_attention(const void* q, int dtype, const void* k_packed, 
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, sigmoid_attention_sum_kernel<bf16>, mgrid, dim3(64), 0, stream,
                          (const float*)part, gate, ldg, (bf16*)out, nh, dv, n_splits);
 }
+
+// The sum of the splits alone (and the gate), for kernels that write the partial outputs themselves.
+TQ_API int tq_sigmoid_attention_sum(const float* part, const float* gate, int ldg, void* out, int dtype, int n_tokens,
+                                    int nh, int dv, int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!part || n_splits < 1) return (int)cudaErrorInvalidValue;
+    const dim3 mgrid(n_tokens, nh);
+    if (dtype == TQ_F32)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, sigmoid_attention_sum_kernel<float>, mgrid, dim3(64), 0, stream, part,
+                             gate, ldg, (float*)out, nh, dv, n_splits);
+    if (dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, sigmoid_attention_sum_kernel<bf16>, mgrid, dim3(64), 0, stream, part,
+                             gate, ldg, (bf16*)out, nh, dv, n_splits);
+    return (int)cudaErrorInvalidValue;
+}

@@ -22,8 +22,11 @@ from typing import IO, Iterable
 
 import numpy as np
 
+from ..cache import PAGE_TOKENS
 from .batch import StepRow
 from .engine import Engine
+
+SLACK_PAGES = 32
 
 
 class TraceError(ValueError):
@@ -80,9 +83,11 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens)
+    # the cache keeps whole pages: every live request may leave most of a page unused, so a few pages are added
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device,
+                                max_tokens=args.max_tokens + SLACK_PAGES * PAGE_TOKENS)
     replay(engine, sys.stdin, args.out)
     return 0

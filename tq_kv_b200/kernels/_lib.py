@@ -194,6 +194,9 @@ _SIGNATURES = {
     "tq_sigmoid_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int,
                               c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p,
                               c_int, c_int, c_int, c_void_p, c_void_p],
+    "tq_sigmoid_flash_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_sigmoid_attention_sum": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p,
                   c_void_p, c_void_p],
     "tq_sample_seeded": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, ctypes.c_ulonglong, c_int,

@@ -114,6 +114,18 @@ def sigmoid_attention(q: torch.Tensor, out: torch.Tensor, *, n_heads: int, n_kv_
         if st != NOT_SUPPORTED:
             check(st, "sigmoid_prefill_tc")
             return out
+    if USE_TC_ATTENTION and not packed and q.dtype == torch.bfloat16 and key_dim == value_dim:
+        # the cache streamed once for all heads of a group (csrc/flash_decode.cu with sigmoid weights)
+        st = core().tq_sigmoid_flash_decode(
+            ptr(q), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width, page_tokens, ptr(tok_pos), ptr(tok_seq),
+            float(scale), ptr(bias), n_dist, ptr(gate), ldg, ptr(out), ptr(part), T, n_heads, n_kv_heads, key_dim,
+            n_splits, stream())
+        if st != NOT_SUPPORTED:
+            check(st, "sigmoid_flash_decode")
+            if n_splits > 1:
+                check(core().tq_sigmoid_attention_sum(ptr(part), ptr(gate), ldg, ptr(out), dtype_code(out), T, n_heads,
+                                                      value_dim, n_splits, stream()), "sigmoid_attention_sum")
+            return out
     check(core().tq_sigmoid_attention(
         ptr(q), dtype_code(q), ptr(k_packed), ptr(v_packed), ptr(k_pages), ptr(v_pages), ptr(block_table), table_width,
         page_tokens, ptr(tok_pos), ptr(tok_seq), ptr(cu_seqlens), ptr(start_pos), float(scale), ptr(bias), n_dist,
