@@ -87,7 +87,11 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     # the cache keeps whole pages: every live request may leave most of a page unused, so a few pages are added
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device,
-                                max_tokens=args.max_tokens + SLACK_PAGES * PAGE_TOKENS)
+    # (no single request is longer than --max-tokens: that stays the context limit)
+    from ..config import read_config_json, spec_from_config_dict
+    positions = spec_from_config_dict(read_config_json(args.model))[2].max_positions
+    limit = min(positions, -(-args.max_tokens // PAGE_TOKENS) * PAGE_TOKENS)
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_context=limit,
+                                max_tokens=limit + SLACK_PAGES * PAGE_TOKENS)
     replay(engine, sys.stdin, args.out)
     return 0
