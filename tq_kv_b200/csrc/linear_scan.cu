@@ -24,7 +24,9 @@
 //                grid (sequence, head, column tile).
 // linear_step    steps in which every sequence brings one token (decoding): the state is all the traffic, so a
 //                warp owns 32 neighbouring columns and a slice of the keys (whole 128-byte rows of the state per
-//                load), and the slices meet in shared memory.  grid (sequence, head, column tile of 32).
+//                load), and the slices meet in shared memory.  It makes the token's vectors itself (what
+//                scan_prepare does for the scan), so a decode step is one launch.
+//                grid (sequence, head, column tile of 32).
 #include "common.cuh"
 
 #define SCAN_DECAY 0
@@ -50,6 +52,8 @@ struct ScanArgs {
     int H, d, e;
     int chunk;                // tokens staged at a time
     int vec;                  // every vector starts on a 16-byte boundary and d, e are multiples of four
+    int silu;                 // linear_step, SCAN_DECAY: q, k, v pass through silu (nothing was prepared)
+    float unit_eps;           // linear_step, SCAN_DELTA: au and w hold the logits still (nothing was prepared)
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
@@ -375,7 +379,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
     float* su = sk + d;
     float* sau = su + d;
     float* sw = sau + d;
-    float* red = sm + (MODE == SCAN_DELTA ? 5 : 2) * d;       // [2][4][32]
+    float* red = sm + (MODE == SCAN_DELTA ? 5 : 2) * d;       // [4] + pad, then [2][4][32]
     pdl_wait();
     pdl_launch();
     const int t = a.cu_seqlens[b];
@@ -387,16 +391,32 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
         const int key = i * 4 + warp;
         S[i] = (col_ok && key < d) ? st[(size_t)key * e + col] : 0.f;
     }
+    // the token's vectors, made here from the projections' results (one token: no prepare kernel runs before)
+    float ss = 0.f;
     for (int i = tid; i < d; i += SCAN_THREADS) {
-        sq[i] = a.q[(size_t)t * a.ldp + head * d + i];
-        sk[i] = a.k[(size_t)t * a.ldp + head * d + i];
+        float qv = a.q[(size_t)t * a.ldp + head * d + i], kv = a.k[(size_t)t * a.ldp + head * d + i];
+        if (MODE == SCAN_DECAY && a.silu) { qv = siluf_(qv); kv = siluf_(kv); }
+        sq[i] = qv;
+        sk[i] = kv;
         if (MODE == SCAN_DELTA) {
-            su[i] = a.u[(size_t)t * a.ldu + head * d + i];
-            sau[i] = a.au[(size_t)t * a.ldp + head * d + i];
-            sw[i] = a.w[(size_t)t * a.ldw + head * d + i];
+            ss = fmaf(kv, kv, ss);
+            sau[i] = sigmoidf_(a.au[(size_t)t * a.ldp + head * d + i]);
+            sw[i] = expf(-0.6065306597126334f * sigmoidf_(a.w[(size_t)t * a.ldw + head * d + i]));
         }
     }
-    const float vj = col_ok ? a.v[(size_t)t * a.ldp + head * e + col] : 0.f;
+    float vj = col_ok ? a.v[(size_t)t * a.ldp + head * e + col] : 0.f;
+    if (MODE == SCAN_DECAY && a.silu) vj = siluf_(vj);
+    if (MODE == SCAN_DELTA) {
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        const float inv = 1.f / sqrtf((red[0] + red[1]) + (red[2] + red[3]) + a.unit_eps);
+        for (int i = tid; i < d; i += SCAN_THREADS) {       // (each thread rewrites the entries it wrote)
+            const float uu = sk[i] * inv;
+            su[i] = uu;
+            sau[i] = -(sau[i] * uu);
+        }
+    }
     __syncthreads();
     float dot = 0.f;
     if (MODE == SCAN_DELTA) {
@@ -405,9 +425,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
             const int key = i * 4 + warp;
             if (key < d) dot = fmaf(su[key], S[i], dot);
         }
-        red[warp * 32 + lane] = dot;
+        red[128 + warp * 32 + lane] = dot;
         __syncthreads();
-        dot = (red[lane] + red[32 + lane]) + (red[64 + lane] + red[96 + lane]);
+        dot = (red[128 + lane] + red[160 + lane]) + (red[192 + lane] + red[224 + lane]);
     }
     float o = 0.f;
     const float c_head = MODE == SCAN_DECAY ? a.head_decay[head] : 0.f;
@@ -421,16 +441,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
             if (col_ok) st[(size_t)key * e + col] = S[i];
         }
     }
-    red[128 + warp * 32 + lane] = o;
+    red[256 + warp * 32 + lane] = o;
     __syncthreads();
     if (warp == 0 && col_ok)
-        a.out[(size_t)t * a.ldo + head * e + col] = (red[128 + lane] + red[160 + lane]) + (red[192 + lane] + red[224 + lane]);
+        a.out[(size_t)t * a.ldo + head * e + col] = (red[256 + lane] + red[288 + lane]) + (red[320 + lane] + red[352 + lane]);
 }
 
 template <int MODE>
 static int dispatch_step(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
     const dim3 grid(n_seqs, a.H, (a.e + 31) / 32);
-    const size_t smem = ((MODE == SCAN_DELTA ? 5 : 2) * (size_t)a.d + 256) * sizeof(float);
+    const size_t smem = ((MODE == SCAN_DELTA ? 5 : 2) * (size_t)a.d + 384) * sizeof(float);
 #define TQ_STEP(K) return tq_launch_pdl(TQ_PDL_ELEMENTWISE, linear_step_kernel<MODE, K>, grid, dim3(SCAN_THREADS), smem, stream, a)
     if (a.d <= 32) TQ_STEP(8);
     if (a.d <= 64) TQ_STEP(16);
@@ -442,7 +462,8 @@ static int dispatch_step(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
 // mode 0 (constant decay per head, head_decay [H]; with `silu` q, k, v first pass through silu, in place) or 1 (the
 // generalised delta rule: w_logit [T, ldw] and the removal logits at a_logit become w and a * u in place, u is
 // scratch [T, ldu]; e == d).  q, k, v, a_logit point into one float32 buffer of row stride ldp.  `single` says that
-// every sequence brings exactly one token.  Key widths up to 256.
+// every sequence brings exactly one token: one kernel then does everything and the buffers are left as they were.
+// Key widths up to 256.
 TQ_API int tq_linear_scan(int mode, float* q, float* k, float* v, float* a_logit, int ldp, float* w_logit, int ldw,
                           float* u, int ldu, const float* head_decay, int silu, float unit_eps, float* state,
                           const int* cu_seqlens, const int* slots, int n_seqs, int n_tokens, int single, float* out,
@@ -450,11 +471,13 @@ TQ_API int tq_linear_scan(int mode, float* q, float* k, float* v, float* a_logit
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (!q || !k || !v || !state || !cu_seqlens || !slots || !out || H <= 0 || H > 65535 || d <= 0 || d > 256 || e <= 0)
         return (int)cudaErrorInvalidValue;
-    ScanArgs a{q, k, v, a_logit, ldp, u, ldu, w_logit, ldw, head_decay, state, cu_seqlens, slots, out, ldo, H, d, e, 0, 0};
+    ScanArgs a{q, k, v, a_logit, ldp, u, ldu, w_logit, ldw, head_decay, state, cu_seqlens, slots, out, ldo, H, d, e, 0, 0,
+               silu, unit_eps};
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     a.vec = (d % 4 == 0 && e % 4 == 0 && ldp % 4 == 0 && al(q) && al(k) && al(v)) ? 1 : 0;
     if (mode == SCAN_DECAY) {
         if (!head_decay) return (int)cudaErrorInvalidValue;
+        if (single) return dispatch_step<SCAN_DECAY>(a, n_seqs, stream);
         if (silu) {
             const int threads = 256;
             for (int part = 0; part < 3; ++part) {
@@ -468,16 +491,18 @@ TQ_API int tq_linear_scan(int mode, float* q, float* k, float* v, float* a_logit
                 if (st) return st;
             }
         }
-        return single ? dispatch_step<SCAN_DECAY>(a, n_seqs, stream) : dispatch_scan<SCAN_DECAY>(a, n_seqs, stream);
+        return dispatch_scan<SCAN_DECAY>(a, n_seqs, stream);
     }
     if (mode == SCAN_DELTA) {
-        if (!w_logit || !a_logit || !u || e != d) return (int)cudaErrorInvalidValue;
+        if (!w_logit || !a_logit || e != d) return (int)cudaErrorInvalidValue;
+        if (single) return dispatch_step<SCAN_DELTA>(a, n_seqs, stream);
+        if (!u) return (int)cudaErrorInvalidValue;
         a.vec = a.vec && ldu % 4 == 0 && ldw % 4 == 0 && al(u) && al(w_logit) && al(a_logit);
         const int rows = n_tokens * H;
         int st = tq_launch_pdl(TQ_PDL_ELEMENTWISE, scan_prepare_delta_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream,
                                (const float*)k, a_logit, ldp, w_logit, ldw, u, ldu, rows, H, d, unit_eps);
         if (st) return st;
-        return single ? dispatch_step<SCAN_DELTA>(a, n_seqs, stream) : dispatch_scan<SCAN_DELTA>(a, n_seqs, stream);
+        return dispatch_scan<SCAN_DELTA>(a, n_seqs, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

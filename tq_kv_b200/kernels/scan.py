@@ -25,7 +25,7 @@ def linear_scan(proj: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tenso
     off_a of proj, the generalised delta rule:
         S_t = diag(w_t) S_{t-1} - (a_t * u_t)(u_t^T S_{t-1}) + k_t v_t^T,
         w = exp(-exp(-1/2) sigmoid(decay_logit)), a = sigmoid(removal logit), u = k / sqrt(|k|^2 + unit_eps).
-    The kernels work in place: afterwards proj holds silu(q | k | v) (first rule, with `silu`) or -(a * u) in
+    Unless `single_tokens`, the kernels work in place: afterwards proj holds silu(q | k | v) (first rule, with `silu`) or -(a * u) in
     place of the removal logits, and decay_logit holds w.  state float32 [slots, heads, d, e] is read at
     slots[b] before the first token and written after the last.  `single_tokens`: every sequence brings
     exactly one token (the kernel built for decoding runs)."""
@@ -54,14 +54,15 @@ def linear_scan(proj: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tenso
         if e != d or off_a + heads * d > ld:
             raise KernelError("linear_scan: the delta rule has square states; removal logits must fit the rows")
         mode, ld_w = SCAN_DELTA, decay_logit.stride(0)
-        u = torch.empty((T, heads * d), dtype=torch.float32, device=proj.device)
-        ld_u = u.stride(0)
+        if not single_tokens:
+            u = torch.empty((T, heads * d), dtype=torch.float32, device=proj.device)
+            ld_u = u.stride(0)
         a = proj[:, off_a:]
     else:
         if head_decay.dtype != torch.float32 or head_decay.shape[0] != heads:
             raise KernelError("linear_scan: head_decay must be float32 [heads]")
         mode = SCAN_DECAY
-    n_kernels = (2 if mode == SCAN_DELTA else (4 if silu else 1))
+    n_kernels = 1 if single_tokens else (2 if mode == SCAN_DELTA else (4 if silu else 1))
     check(core().tq_linear_scan(mode, ptr(proj[:, off_q:]), ptr(proj[:, off_k:]), ptr(proj[:, off_v:]), ptr(a),
                                 proj.stride(0), ptr(decay_logit), ld_w, ptr(u), ld_u, ptr(head_decay), int(silu),
                                 float(unit_eps), ptr(state), ptr(cu_seqlens), ptr(slots), int(n_seqs), T,
