@@ -63,7 +63,18 @@ Z_C = {
         {**_delta(3, 28, 20), "mlp": _ff(64)},
     ],
 }
-CASES = {"a": Z_A, "b": Z_B, "c": Z_C}
+# D: attention heads of 64 and 128 (the widths the tensor-core attention kernels take), five norm groups.
+Z_D = {
+    "architecture": "Zodosun", "vocab": 384, "width": 160, "logit_scale": 0.3, "norm": {"eps": 1e-6, "groups": 5},
+    "layers": [
+        {"type": "parallel", "mlp": None,
+         "mixer": {"left": _left(2, 1, 64, 64, 0.11, 90, 0.4, 10, 24), "right": _right(5, 16, 32, [0.2, 0.5, 0.8, 0.95, 0.999])}},
+        {**_delta(4, 40, 10), "mlp": _ff(96)},
+        {"type": "parallel", "mlp": _ff(192),
+         "mixer": {"left": _left(2, 2, 128, 128, 0.07, 300, 0.15, 50, 40), "right": _right(2, 64, 64, [0.9, 0.99])}},
+    ],
+}
+CASES = {"a": Z_A, "b": Z_B, "c": Z_C, "d": Z_D}
 
 
 def make_weights(cfg: dict, seed: int) -> dict:
