@@ -19,6 +19,10 @@ def test_the_registry_finds_the_architecture_by_its_own_key():
     assert isinstance(cfg, ZodosunConfig) and len(spec.layers) == 4 and spec.vocab_size == 300
     kinds = [l.mixer.kind for l in spec.layers]
     assert kinds == ["side_by_side", "delta_rule_mixer", "delta_rule_mixer", "side_by_side"]
+    from zodosun_cases import Z_E
+    from tq_kv_b200.engine.model import DecoderModel
+    kv, state = DecoderModel(spec_from_config_dict(Z_E)[2]).cache_requests()
+    assert kv == {} and sorted(state) == [0, 1]                  # a model of state mixers only caches no keys
     assert [l.feed_forward is not None for l in spec.layers] == [True, True, False, False]
     assert spec.layers[0].mixer_norm.params["groups"] == 3 and spec.final_norm.params["groups"] == 3
     assert spec.head.params["logit_scale"] == 0.75

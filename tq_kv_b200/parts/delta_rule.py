@@ -32,6 +32,7 @@ _MIN_TC_RANK = 64
 
 
 class DeltaRuleMixer(Mixer):
+    takes_pending_norm = True           # x goes to kernels.linear only
     graph_capturable = True             # slots and lengths are read on the device
 
     def __init__(self, spec):

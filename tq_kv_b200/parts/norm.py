@@ -43,13 +43,13 @@ class GroupRMSNorm(RMSNorm):
     """RMS norm in groups: the row is cut into `groups` equal consecutive
     parts, each divided by its own sqrt(mean(part^2) + eps); then the whole row
     times the weight.  One group is the plain norm."""
-    pending = None                      # the products fold in the plain norm only
-
     def __init__(self, spec):
         super().__init__(spec)
         self.groups = int(self.params.get("groups", 1))
         if self.groups < 1 or self.width % self.groups:
             raise ConfigError(f"a norm over {self.width} values cannot be cut into {self.groups} equal groups")
+        if self.groups > 1:
+            self.pending = None             # the products fold in the plain norm only
 
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]

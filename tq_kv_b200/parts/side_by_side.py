@@ -17,6 +17,7 @@ from .registry import make_part
 
 
 class SideBySideMixer(Mixer):
+    takes_pending_norm = True           # (run once here: the branches share its result)
     def __init__(self, spec):
         super().__init__(spec)
         p = self.params

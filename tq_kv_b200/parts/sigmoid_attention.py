@@ -40,20 +40,23 @@ from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
 
 
 def distance_rows(rows: int, far: int, n_distances: int) -> torch.Tensor:
-    """The table row for every distance 0 .. n_distances - 1 (int64)."""
+    """The table row for every distance 0 .. n_distances - 1 (int64): the distance itself below rows // 2, then
+    min(rows - 1, rows // 2 + floor(ln(n / (rows // 2)) / ln(far / (rows // 2)) * (rows - rows // 2)))."""
     half = rows // 2
     out = []
     for n in range(n_distances):
         if n < half:
             out.append(n)
-        elif half == 0 or far <= half:
-            out.append(rows - 1)
+        elif half == 0 or far == half:                   # the formula divides by zero: everything beyond is the last row
+            out.append(rows - 1 if n > half or half == 0 else half)
         else:
-            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+            b = half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))
+            out.append(max(0, min(rows - 1, b)))
     return torch.tensor(out, dtype=torch.int64)
 
 
 class SigmoidAttention(Mixer):
+    takes_pending_norm = True           # x goes to kernels.linear only
     graph_capturable = True
     padded_rows_ok = True               # causal, and rows past a sequence's new length are not cached
 
@@ -122,7 +125,9 @@ class SigmoidAttention(Mixer):
         if self.distance is not None:
             rel = float32_vector(tensors[self._n("distance")])                       # [B, heads]
             far = int(self.distance["far"])
-            n_dist = max(1, min(runtime.max_context, max(far, rel.shape[0] // 2) + 1))   # later distances share the last
+            # from `far` on every distance has the last row (if the rows widen at all: far beyond the exact ones)
+            n_dist = runtime.max_context if far <= rel.shape[0] // 2 else min(runtime.max_context, far + 1)
+            n_dist = max(1, n_dist)
             rows = distance_rows(rel.shape[0], far, n_dist).to(dev)
             table = rel[rows].t().contiguous()                                       # [heads, n_dist]
         if self.head_offset:
