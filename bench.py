@@ -26,6 +26,11 @@ then 256 decode steps.  Peaks come from MEASURED_PEAKS.json beside this file
 if it exists, else from an earlier measurement on the same kind of machine
 (6.65 TB/s, 1.59 PFLOP/s).
 
+`--design zodosun [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the Zodosun decoder beside the Qwen2
+decoder of the same width, depth, heads, feed-forward and vocabulary (random weights, bfloat16): device time of a
+prompt, of decode steps at batch 8 and 64, and the time by class of kernel with what the attention and scan
+kernels reach of their rooflines, as one JSON line of its own.  The default workload and its line are untouched.
+
 The reference arm (`--impl reference`) cannot run here: the reference is a
 Rust workspace and no Rust toolchain is installed, so it prints its
 `unavailable` line.
