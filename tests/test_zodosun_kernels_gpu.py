@@ -389,3 +389,36 @@ def test_the_one_token_kernel_equals_the_scan(H, d, e):
             states.append(state)
         _close(outs[0], outs[1], 1e-5, mode + " outputs")
         _close(states[0], states[1], 1e-5, mode + " states")
+
+
+@pytest.mark.parametrize("H, G, d", [(4, 2, 32), (2, 2, 64), (3, 1, 96), (8, 2, 128), (34, 2, 64), (2, 1, 48)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sigmoid_attention_of_single_decoded_tokens(H, G, d, dtype):
+    """Rows of one token each (what a decode step brings) at several positions of the same cached keys, with one
+    split and with several: the kernel that streams the cache once for a group's heads (bfloat16, widths 32 to 128,
+    up to 16 heads a group) and the general one (everything else) against float64."""
+    from tq_kv_b200 import kernels
+    torch.manual_seed(H * d)
+    T, scale, n_dist = 200, 0.25 / math.sqrt(d), 57
+    q = torch.randn(T, H * d, device=DEV).to(dtype)
+    k = torch.randn(T, G * d, device=DEV).to(dtype)
+    v = torch.randn(T, G * d, device=DEV).to(dtype)
+    bias = torch.randn(H, n_dist, device=DEV) * 2 - 1
+    gate = torch.randn(T, H, device=DEV)
+    want = _attention_reference(q, k, v, H, G, d, d, scale, bias, gate)
+    order = [3, 1, 0, 2]
+    kp, vp = _pages(k, v, G, d, d, 64, order)
+    rows = [199, 0, 63, 64, 128, 31]
+    table = _i32(order * len(rows))
+    pos = _i32(rows)
+    sel = torch.tensor(rows, device=DEV)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for n_splits in (1, 4):
+        out = torch.full((len(rows), H * d), float("nan"), dtype=dtype, device=DEV)
+        scratch = torch.empty(len(rows) * H * n_splits * d, device=DEV) if n_splits > 1 else None
+        kernels.sigmoid_attention(q[sel].contiguous(), out, n_heads=H, n_kv_heads=G, key_dim=d, value_dim=d, scale=scale,
+                                  tok_pos=pos, tok_seq=_i32(list(range(len(rows)))),
+                                  cu_seqlens=_i32(list(range(len(rows) + 1))), start_pos=pos, bias=bias,
+                                  gate=gate[sel].contiguous(), k_pages=kp, v_pages=vp, block_table=table, table_width=4,
+                                  page_tokens=64, n_splits=n_splits, scratch=scratch)
+        _close(out, want[sel.cpu()], tol, f"{n_splits} splits")
