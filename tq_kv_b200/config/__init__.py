@@ -5,6 +5,9 @@ from .qwen2 import MODEL_TYPE as QWEN2_MODEL_TYPE
 from .qwen2 import Qwen2Config, build_qwen2_spec, read_config_json
 from .registry import (Architecture, register_architecture, registered_architectures, resolve,
                        spec_from_config_dict, unregister_architecture)
+from .rirudra import ARCHITECTURE as RIRUDRA_ARCHITECTURE
+from .rirudra import MODEL_TYPE as RIRUDRA_MODEL_TYPE
+from .rirudra import RirudraConfig, build_rirudra_spec
 from .shapes import named_shape, shape_names
 from .zodosun import ARCHITECTURE as ZODOSUN_ARCHITECTURE
 from .zodosun import MODEL_TYPE as ZODOSUN_MODEL_TYPE
@@ -16,7 +19,11 @@ register_architecture(
 register_architecture(
     Architecture(ZODOSUN_ARCHITECTURE, ZODOSUN_MODEL_TYPE, ZodosunConfig, build_zodosun_spec), replace=True)
 
+register_architecture(
+    Architecture(RIRUDRA_ARCHITECTURE, RIRUDRA_MODEL_TYPE, RirudraConfig, build_rirudra_spec), replace=True)
+
 __all__ = [
+    "RirudraConfig", "build_rirudra_spec",
     "Architecture", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "Qwen2Config", "ScheduleEntry",
     "ZodosunConfig", "build_zodosun_spec",
     "build_qwen2_spec", "named_shape", "read_config_json", "register_architecture",

@@ -10,7 +10,7 @@
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int H, int V, int* status) {
+                             float* __restrict__ out, int H, int V, int* status, float scale) {
     const int t = blockIdx.x;
     pdl_wait();
     pdl_launch();
@@ -22,20 +22,26 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
         return;
     }
     const TW* row = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<TW>(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32<TW>(row[i]) * scale;
 }
 
-TQ_API int tq_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int H, int V,
-                    int* status, cudaStream_t stream) {
+// out[t] = scale * table[tokens[t]] (a model that multiplies its embeddings by a constant; 1 for the others)
+TQ_API int tq_embed_scaled(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int H, int V,
+                           int* status, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == TQ_F32)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
-                             (const float*)table, out, H, V, status);
+                             (const float*)table, out, H, V, status, scale);
     if (table_dtype == TQ_BF16)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
-                             (const bf16*)table, out, H, V, status);
+                             (const bf16*)table, out, H, V, status, scale);
     return (int)cudaErrorInvalidValue;
+}
+
+TQ_API int tq_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int H, int V,
+                    int* status, cudaStream_t stream) {
+    return tq_embed_scaled(tokens, table, table_dtype, out, n_tokens, H, V, status, 1.f, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -503,7 +509,7 @@ TQ_API int tq_embed_sinusoid(const int* tokens, const int* positions, const void
 template <typename TO>
 __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
                                      const float* __restrict__ gate, int ldg, TO* __restrict__ out, int ldo,
-                                     const int* __restrict__ rows, int gw, float eps) {
+                                     const int* __restrict__ rows, int gw, float eps, int gate_mode) {
     __shared__ float red[32];
     const int r = blockIdx.x, g = blockIdx.y;
     pdl_wait();
@@ -513,34 +519,42 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ x, int ldx, const
     const float* wr = w + (size_t)g * gw;
     const float* gr = gate ? gate + (size_t)src * ldg + (size_t)g * gw : nullptr;
     TO* o = out + (size_t)r * ldo + (size_t)g * gw;
+    // gate_mode 0: times sigmoid(gate) after the norm; 1: times silu(gate) after the norm; 2: times silu(gate)
+    // before it (the norm then sees the gated values)
+    const bool before = gr && gate_mode == 2;
     float ss = 0.f;
     for (int i = threadIdx.x; i < gw; i += blockDim.x) {
-        const float v = xr[i];
+        float v = xr[i];
+        if (before) v *= gr[i] / (1.f + expf(-gr[i]));
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, red);
     const float rms = sqrtf(ss / (float)gw + eps);
     for (int i = threadIdx.x; i < gw; i += blockDim.x) {
-        float y = (xr[i] / rms) * wr[i];
-        if (gr) y *= 1.f / (1.f + expf(-gr[i]));
+        float v = xr[i];
+        if (before) v *= gr[i] / (1.f + expf(-gr[i]));
+        float y = (v / rms) * wr[i];
+        if (gr && gate_mode == 0) y *= 1.f / (1.f + expf(-gr[i]));
+        if (gr && gate_mode == 1) y *= gr[i] / (1.f + expf(-gr[i]));
         o[i] = from_f32<TO>(y);
     }
 }
 
 TQ_API int tq_group_rmsnorm(const float* x, int ldx, const float* w, const float* gate, int ldg, void* out,
                             int out_dtype, int ldo, const int* rows, int n_rows, int width, int groups, float eps,
-                            cudaStream_t stream) {
+                            int gate_mode, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (groups <= 0 || groups > 65535 || width <= 0 || width % groups) return (int)cudaErrorInvalidValue;
+    if (groups <= 0 || groups > 65535 || width <= 0 || width % groups || gate_mode < 0 || gate_mode > 2)
+        return (int)cudaErrorInvalidValue;
     const int gw = width / groups;
     const int threads = gw >= 2048 ? 512 : (gw >= 512 ? 256 : (gw > 64 ? 128 : 64));
     const dim3 grid(n_rows, groups);
     if (out_dtype == TQ_F32)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, group_rmsnorm_kernel<float>, grid, dim3(threads), 0, stream, x, ldx, w,
-                             gate, ldg, (float*)out, ldo, rows, gw, eps);
+                             gate, ldg, (float*)out, ldo, rows, gw, eps, gate_mode);
     if (out_dtype == TQ_BF16)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, group_rmsnorm_kernel<bf16>, grid, dim3(threads), 0, stream, x, ldx, w,
-                             gate, ldg, (bf16*)out, ldo, rows, gw, eps);
+                             gate, ldg, (bf16*)out, ldo, rows, gw, eps, gate_mode);
     return (int)cudaErrorInvalidValue;
 }
 
@@ -619,6 +633,39 @@ TQ_API int tq_tanh_rows(const float* x, int ldx, void* out, int out_dtype, int l
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, tanh_rows_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, x,
                              ldx, (bf16*)out, ldo, n, total);
     return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// acc[i] += s * x[i], all float32: the residual sum of a layer whose sublayers' results are added together and
+// enter the stream times a constant.
+// ---------------------------------------------------------------------------
+__global__ void add_scaled_kernel(float* __restrict__ acc, const float* __restrict__ x, size_t total, float s) {
+    pdl_wait();
+    pdl_launch();
+    if ((total & 3) == 0) {
+        float4* a4 = reinterpret_cast<float4*>(acc);
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total / 4;
+             idx += (size_t)gridDim.x * blockDim.x) {
+            float4 a = a4[idx];
+            const float4 v = x4[idx];
+            a.x = fmaf(s, v.x, a.x); a.y = fmaf(s, v.y, a.y); a.z = fmaf(s, v.z, a.z); a.w = fmaf(s, v.w, a.w);
+            a4[idx] = a;
+        }
+        return;
+    }
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        acc[idx] = fmaf(s, x[idx], acc[idx]);
+}
+
+TQ_API int tq_add_scaled(float* acc, const float* x, size_t total, float s, cudaStream_t stream) {
+    if (total == 0) return 0;
+    const int threads = 256;
+    size_t blocks = (total / 4 + threads) / threads;
+    if (blocks > (size_t)tq_sm_count() * 16) blocks = (size_t)tq_sm_count() * 16;
+    return tq_launch_pdl(TQ_PDL_ELEMENTWISE, add_scaled_kernel, dim3((int)blocks), dim3(threads), 0, stream, acc, x, total,
+                         s);
 }
 
 // ---------------------------------------------------------------------------

@@ -6,7 +6,14 @@
 //   SCAN_DELTA   S_t = diag(w_t) S_{t-1} - (a_t * u_t)(u_t^T S_{t-1}) + k_t v_t^T
 //                with u_t = k_t / sqrt(|k_t|^2 + unit_eps)                (the generalised delta rule: a decay per
 //                key channel, and the removal of what the state holds along the unit key, at a rate per channel)
-//   o_t = S_t^T q_t  in both.
+//   SCAN_GATED   S_t = g_t S_{t-1} + k_t (dt_t v_t)^T,  o_t = S_t^T q_t + skip_head * v_t
+//                (one decay g and one step size dt per head and token; several heads may share q and k)
+//   SCAN_GATED_DELTA   S' = g_t S_{t-1};  u = beta_t (v_t - S'^T k_t);  S_t = S' + k_t u^T
+//                (the delta rule with one decay and one write strength per head and token: the state first
+//                fades, then what it holds along k_t is replaced by v_t at the rate beta_t)
+//   o_t = S_t^T q_t  in all.  The last two take their per-token scalars ready-made ([T, H, 4] floats: g, then
+//   dt or beta), the value columns may be narrower or wider than the keys, and head h reads the q/k vectors of
+//   head h / qk_div.
 //
 // Everything here is float32: the state, and all that enters the recurrence.  Three kernels:
 //
@@ -31,6 +38,8 @@
 
 #define SCAN_DECAY 0
 #define SCAN_DELTA 1
+#define SCAN_GATED 2
+#define SCAN_GATED_DELTA 3
 #define SCAN_THREADS 128      // of the one-token kernel
 
 struct ScanArgs {
@@ -54,6 +63,10 @@ struct ScanArgs {
     int vec;                  // every vector starts on a 16-byte boundary and d, e are multiples of four
     int silu;                 // linear_step, SCAN_DECAY: q, k, v pass through silu (nothing was prepared)
     float unit_eps;           // linear_step, SCAN_DELTA: au and w hold the logits still (nothing was prepared)
+    const float* scal;        // SCAN_GATED*: [T, H, 4] per token and head: decay, then step size or write strength
+    const float* skip;        // SCAN_GATED: [H] or null, o += skip_head * v
+    int qk_div;               // head h reads the q/k vectors of head h / qk_div
+    size_t state_stride;      // floats from one slot's states to the next
 };
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
@@ -115,12 +128,14 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
     constexpr int DP = KG * RK;
     constexpr int CT = THREADS / KG * RC;
     constexpr int NV = MODE == SCAN_DELTA ? 5 : 2;
+    constexpr int SC = MODE >= SCAN_GATED ? 4 : 0;          // a token's scalars, in front of a stage
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * CT;
+    const int hq = head / a.qk_div;
     const int tid = threadIdx.x, kg = tid % KG, cg = tid / KG;
     const int colb = col0 + cg * RC;           // this thread's first column
     const int d = a.d, e = a.e, TC = a.chunk;
-    const int stage_floats = TC * (NV * DP + CT);
+    const int stage_floats = TC * (SC + NV * DP + CT);
     float* so = sm + 2 * stage_floats;         // [TC][CT] outputs of a chunk
     // the padding (keys d .. DP-1, columns past e) stays zero: q, k, u and a*u of a key that does not exist
     for (int i = tid; i < 2 * stage_floats; i += THREADS) sm[i] = 0.f;
@@ -129,7 +144,7 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
     pdl_launch();
     const int t0 = a.cu_seqlens[b], t1 = a.cu_seqlens[b + 1];
     const int slot = a.slots[b];
-    float* st = a.state + ((size_t)slot * a.H + head) * (size_t)d * e;
+    float* st = a.state + (size_t)slot * a.state_stride + (size_t)head * d * e;
     float2 S[RK / 2][RC];                      // S[r][c] = keys 2r and 2r + 1 of this thread, column c
 #pragma unroll
     for (int r = 0; r < RK; ++r) {
@@ -141,22 +156,33 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
         }
     }
     const float c_head = MODE == SCAN_DECAY ? a.head_decay[head] : 0.f;
+    const float skip = (MODE == SCAN_GATED && a.skip) ? a.skip[head] : 0.f;
     __syncthreads();
 
     // stage s holds, token by token: q[DP] k[DP] (u[DP] au[DP] w[DP]) and after all of them v[TC][CT]
     auto stage_in = [&](int base, int s) {
         const int n = min(TC, t1 - base);
-        float* dst = sm + s * stage_floats;
+        float* dsc = sm + s * stage_floats;
+        float* dst = dsc + TC * SC;
         float* dv = dst + TC * NV * DP;
         const int cols = min(CT, e - col0);
+        if (SC) {
+            if (a.vec) {
+                for (int tt = tid; tt < n; tt += THREADS)
+                    cp_async16(dsc + tt * 4, a.scal + ((size_t)(base + tt) * a.H + head) * 4);
+            } else {
+                for (int idx = tid; idx < n * 2; idx += THREADS)
+                    dsc[(idx >> 1) * 4 + (idx & 1)] = a.scal[((size_t)(base + (idx >> 1)) * a.H + head) * 4 + (idx & 1)];
+            }
+        }
         if (a.vec) {
             const int d4 = d >> 2, c4 = cols >> 2;
             for (int idx = tid; idx < n * d4; idx += THREADS) {
                 const int tt = idx / d4, i = (idx - tt * d4) * 4;
                 const size_t t = (size_t)(base + tt);
                 float* row = dst + tt * NV * DP + i;
-                cp_async16(row, a.q + t * a.ldp + head * d + i);
-                cp_async16(row + DP, a.k + t * a.ldp + head * d + i);
+                cp_async16(row, a.q + t * a.ldp + hq * d + i);
+                cp_async16(row + DP, a.k + t * a.ldp + hq * d + i);
                 if (MODE == SCAN_DELTA) {
                     cp_async16(row + 2 * DP, a.u + t * a.ldu + head * d + i);
                     cp_async16(row + 3 * DP, a.au + t * a.ldp + head * d + i);
@@ -172,8 +198,8 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
                 const int tt = idx / d, i = idx - tt * d;
                 const size_t t = (size_t)(base + tt);
                 float* row = dst + tt * NV * DP + i;
-                row[0] = a.q[t * a.ldp + head * d + i];
-                row[DP] = a.k[t * a.ldp + head * d + i];
+                row[0] = a.q[t * a.ldp + hq * d + i];
+                row[DP] = a.k[t * a.ldp + hq * d + i];
                 if (MODE == SCAN_DELTA) {
                     row[2 * DP] = a.u[t * a.ldu + head * d + i];
                     row[3 * DP] = a.au[t * a.ldp + head * d + i];
@@ -199,7 +225,8 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
-        const float* src = sm + s * stage_floats;
+        const float* ssc = sm + s * stage_floats;
+        const float* src = ssc + TC * SC;
         const float* sv = src + TC * NV * DP;
 #pragma unroll 2
         for (int tt = 0; tt < n; ++tt) {
@@ -207,9 +234,11 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
             // time (fma.rn.f32x2: each half is the IEEE fused multiply-add of the scalar instruction).
             const float4* pq = reinterpret_cast<const float4*>(src + tt * NV * DP) + kg;
             float2 vv[RC];
+            float xr[RC];
 #pragma unroll
             for (int c = 0; c < RC; ++c) {
                 const float x = sv[tt * CT + cg * RC + c];
+                xr[c] = x;
                 vv[c] = make_float2(x, x);
             }
             float2 kk[RK / 2], qq[RK / 2];
@@ -254,8 +283,40 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
                         o2[c] = __ffma2_rn(qq[r], S[r][c], o2[c]);
                     }
                 }
+            } else if (MODE == SCAN_GATED_DELTA) {
+                const float g = ssc[tt * 4], beta = ssc[tt * 4 + 1];
+                const float2 gg = make_float2(g, g);
+                float dot[RC];
+#pragma unroll
+                for (int c = 0; c < RC; ++c) {
+                    float2 acc = __fmul2_rn(kk[0], S[0][c]);
+#pragma unroll
+                    for (int r = 1; r < RK / 2; ++r) acc = __ffma2_rn(kk[r], S[r][c], acc);
+                    dot[c] = acc.x + acc.y;
+                }
+#pragma unroll
+                for (int off = KG / 2; off > 0; off >>= 1) {
+#pragma unroll
+                    for (int c = 0; c < RC; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], off);
+                }
+#pragma unroll
+                for (int c = 0; c < RC; ++c) {
+                    const float u = beta * (xr[c] - g * dot[c]);       // what is written along k: the faded state's
+                    const float2 uu = make_float2(u, u);               // reading is taken out, the value put in
+#pragma unroll
+                    for (int r = 0; r < RK / 2; ++r) {
+                        S[r][c] = __ffma2_rn(gg, S[r][c], __fmul2_rn(kk[r], uu));
+                        o2[c] = __ffma2_rn(qq[r], S[r][c], o2[c]);
+                    }
+                }
             } else {
-                const float2 cc = make_float2(c_head, c_head);
+                float2 cc = make_float2(c_head, c_head);
+                if (MODE == SCAN_GATED) {
+                    const float g = ssc[tt * 4], dt = ssc[tt * 4 + 1];
+                    cc = make_float2(g, g);
+#pragma unroll
+                    for (int c = 0; c < RC; ++c) vv[c] = make_float2(dt * xr[c], dt * xr[c]);
+                }
 #pragma unroll
                 for (int c = 0; c < RC; ++c) {
 #pragma unroll
@@ -279,17 +340,20 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
                 float sum = (high ? a1 : a0) + r2;            // column (odd ? 2 : 0) + (high ? 1 : 0)
 #pragma unroll
                 for (int off = 4; off < KG; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (MODE == SCAN_GATED) sum = fmaf(skip, odd ? (high ? xr[3] : xr[2]) : (high ? xr[1] : xr[0]), sum);
                 if (kg < 4) so[tt * CT + cg * RC + (odd ? 2 : 0) + (high ? 1 : 0)] = sum;
             } else if constexpr (RC == 2) {
                 const bool odd = kg & 1;
                 float sum = (odd ? o[1] : o[0]) + __shfl_xor_sync(0xffffffffu, odd ? o[0] : o[1], 1);
 #pragma unroll
                 for (int off = 2; off < KG; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (MODE == SCAN_GATED) sum = fmaf(skip, odd ? xr[1] : xr[0], sum);
                 if (kg < 2) so[tt * CT + cg * RC + (odd ? 1 : 0)] = sum;
             } else {
                 float sum = o[0];
 #pragma unroll
                 for (int off = KG / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (MODE == SCAN_GATED) sum = fmaf(skip, xr[0], sum);
                 if (kg == 0) so[tt * CT + cg] = sum;
             }
         }
@@ -314,9 +378,9 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
 
 template <int MODE, int KG, int THREADS, int RC>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
-    constexpr int CT = THREADS / KG * RC, DP = KG * 8, NV = MODE == SCAN_DELTA ? 5 : 2;
+    constexpr int CT = THREADS / KG * RC, DP = KG * 8, NV = MODE == SCAN_DELTA ? 5 : 2, SC = MODE >= SCAN_GATED ? 4 : 0;
     ScanArgs args = a;
-    const int per_token = 2 * (NV * DP + CT) + CT;       // two stages and the outputs
+    const int per_token = 2 * (SC + NV * DP + CT) + CT;  // two stages and the outputs
     int chunk = 8;
     while (chunk > 1 && (size_t)chunk * per_token * sizeof(float) > SCAN_SMEM_LIMIT) chunk >>= 1;
     args.chunk = chunk;
@@ -373,6 +437,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
     const int b = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int d = a.d, e = a.e, col = col0 + lane;
+    const int hq = head / a.qk_div;
     const bool col_ok = col < e;
     float* sq = sm;                 // [d] each: q k (u au w)
     float* sk = sq + d;
@@ -384,7 +449,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
     pdl_launch();
     const int t = a.cu_seqlens[b];
     const int slot = a.slots[b];
-    float* st = a.state + ((size_t)slot * a.H + head) * (size_t)d * e;
+    float* st = a.state + (size_t)slot * a.state_stride + (size_t)head * d * e;
     float S[KPW];
 #pragma unroll
     for (int i = 0; i < KPW; ++i) {
@@ -394,7 +459,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
     // the token's vectors, made here from the projections' results (one token: no prepare kernel runs before)
     float ss = 0.f;
     for (int i = tid; i < d; i += SCAN_THREADS) {
-        float qv = a.q[(size_t)t * a.ldp + head * d + i], kv = a.k[(size_t)t * a.ldp + head * d + i];
+        float qv = a.q[(size_t)t * a.ldp + hq * d + i], kv = a.k[(size_t)t * a.ldp + hq * d + i];
         if (MODE == SCAN_DECAY && a.silu) { qv = siluf_(qv); kv = siluf_(kv); }
         sq[i] = qv;
         sk[i] = kv;
@@ -419,32 +484,44 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_step_kernel(ScanArgs a) {
     }
     __syncthreads();
     float dot = 0.f;
-    if (MODE == SCAN_DELTA) {
+    float g = 0.f, s2 = 0.f;            // SCAN_GATED*: the token's decay, and its step size or write strength
+    if (MODE >= SCAN_GATED) {
+        g = a.scal[((size_t)t * a.H + head) * 4];
+        s2 = a.scal[((size_t)t * a.H + head) * 4 + 1];
+    }
+    if (MODE == SCAN_DELTA || MODE == SCAN_GATED_DELTA) {
+        const float* sd = MODE == SCAN_DELTA ? su : sk;
 #pragma unroll
         for (int i = 0; i < KPW; ++i) {
             const int key = i * 4 + warp;
-            if (key < d) dot = fmaf(su[key], S[i], dot);
+            if (key < d) dot = fmaf(sd[key], S[i], dot);
         }
         red[128 + warp * 32 + lane] = dot;
         __syncthreads();
         dot = (red[128 + lane] + red[160 + lane]) + (red[192 + lane] + red[224 + lane]);
     }
     float o = 0.f;
-    const float c_head = MODE == SCAN_DECAY ? a.head_decay[head] : 0.f;
+    const float c_head = MODE == SCAN_DECAY ? a.head_decay[head] : g;
+    float vw = vj;                      // what is written along the key
+    if (MODE == SCAN_GATED) vw = s2 * vj;
+    if (MODE == SCAN_GATED_DELTA) vw = s2 * (vj - g * dot);
 #pragma unroll
     for (int i = 0; i < KPW; ++i) {
         const int key = i * 4 + warp;
         if (key < d) {
             if (MODE == SCAN_DELTA) S[i] = fmaf(sw[key], S[i], fmaf(sk[key], vj, sau[key] * dot));
-            else S[i] = fmaf(c_head, S[i], sk[key] * vj);
+            else S[i] = fmaf(c_head, S[i], sk[key] * vw);
             o = fmaf(sq[key], S[i], o);
             if (col_ok) st[(size_t)key * e + col] = S[i];
         }
     }
     red[256 + warp * 32 + lane] = o;
     __syncthreads();
-    if (warp == 0 && col_ok)
-        a.out[(size_t)t * a.ldo + head * e + col] = (red[256 + lane] + red[288 + lane]) + (red[320 + lane] + red[352 + lane]);
+    if (warp == 0 && col_ok) {
+        float sum = (red[256 + lane] + red[288 + lane]) + (red[320 + lane] + red[352 + lane]);
+        if (MODE == SCAN_GATED && a.skip) sum = fmaf(a.skip[head], vj, sum);
+        a.out[(size_t)t * a.ldo + head * e + col] = sum;
+    }
 }
 
 template <int MODE>
@@ -472,7 +549,7 @@ TQ_API int tq_linear_scan(int mode, float* q, float* k, float* v, float* a_logit
     if (!q || !k || !v || !state || !cu_seqlens || !slots || !out || H <= 0 || H > 65535 || d <= 0 || d > 256 || e <= 0)
         return (int)cudaErrorInvalidValue;
     ScanArgs a{q, k, v, a_logit, ldp, u, ldu, w_logit, ldw, head_decay, state, cu_seqlens, slots, out, ldo, H, d, e, 0, 0,
-               silu, unit_eps};
+               silu, unit_eps, nullptr, nullptr, 1, (size_t)H * d * e};
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     a.vec = (d % 4 == 0 && e % 4 == 0 && ldp % 4 == 0 && al(q) && al(k) && al(v)) ? 1 : 0;
     if (mode == SCAN_DECAY) {
@@ -505,4 +582,29 @@ TQ_API int tq_linear_scan(int mode, float* q, float* k, float* v, float* a_logit
         return dispatch_scan<SCAN_DELTA>(a, n_seqs, stream);
     }
     return (int)cudaErrorInvalidValue;
+}
+
+// The rules with one decay per head and token.  q, k [T, ldp] with H / qk_div heads of d, v [T, ldp] with H heads of
+// e, all in one float32 buffer and ready (activations, unit lengths and scales applied); scal [T, H, 4] holds each
+// token's decay and, with `delta`, its write strength beta (S' = g S; S = S' + k (beta (v - S'^T k))^T), else its
+// step size dt (S = g S + k (dt v)^T, o += skip_head * v if skip is given).  state points at the first slot's
+// [H, d, e] block; state_stride floats lie between slots.  `single`: one token per sequence.
+TQ_API int tq_gated_scan(int delta, const float* q, const float* k, const float* v, int ldp, const float* scal,
+                         const float* skip, int qk_div, float* state, long long state_stride, const int* cu_seqlens,
+                         const int* slots, int n_seqs, int n_tokens, int single, float* out, int ldo, int H, int d,
+                         int e, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
+    if (!q || !k || !v || !scal || !state || !cu_seqlens || !slots || !out || H <= 0 || H > 65535 || d <= 0 || d > 256 ||
+        e <= 0 || qk_div <= 0 || H % qk_div || state_stride < (long long)H * d * e)
+        return (int)cudaErrorInvalidValue;
+    ScanArgs a{q, k, v, nullptr, ldp, nullptr, 0, nullptr, 0, nullptr, state, cu_seqlens, slots, out, ldo, H, d, e, 0, 0,
+               0, 0.f, scal, skip, qk_div, (size_t)state_stride};
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    a.vec = (d % 4 == 0 && e % 4 == 0 && ldp % 4 == 0 && al(q) && al(k) && al(v) && al(scal)) ? 1 : 0;
+    if (delta) {
+        if (single) return dispatch_step<SCAN_GATED_DELTA>(a, n_seqs, stream);
+        return dispatch_scan<SCAN_GATED_DELTA>(a, n_seqs, stream);
+    }
+    if (single) return dispatch_step<SCAN_GATED>(a, n_seqs, stream);
+    return dispatch_scan<SCAN_GATED>(a, n_seqs, stream);
 }

@@ -177,7 +177,21 @@ _SIGNATURES = {
     "tq_attention_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tq_embed_sinusoid": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "tq_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
-                         c_float, c_void_p],
+                         c_float, c_int, c_void_p],
+    "tq_embed_scaled": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
+    "tq_add_scaled": [c_void_p, c_void_p, c_size_t, c_float, c_void_p],
+    "tq_gated_scan": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong,
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tq_short_conv": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_void_p,
+                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "tq_latent_rows": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                       c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_void_p],
+    "tq_latent_query": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                        c_void_p, c_int, c_int, c_void_p],
+    "tq_latent_expand": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                         c_void_p],
     "tq_add_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_int, c_float, c_float, c_void_p],
     "tq_scale_inplace": [c_void_p, c_size_t, c_float, c_void_p],

@@ -8,8 +8,9 @@ import torch
 from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
-    """out[t] = float32(table[tokens[t]]).  tokens int32 [T]; table [V, H]
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None,
+          scale: float = 1.0):
+    """out[t] = scale * float32(table[tokens[t]]).  tokens int32 [T]; table [V, H]
     float32 or bfloat16; out float32 [T, H].  `status` (int32 [1]) gets bit 0
     set if a token id lies outside the table."""
     T = tokens.shape[0]
@@ -17,8 +18,8 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: 
     if tokens.dtype != torch.int32 or out.dtype != torch.float32 or tuple(out.shape) != (T, H):
         raise KernelError("embed: tokens must be int32 [T] and out float32 [T, H]")
     need_contiguous(tokens=tokens, table=table, out=out)
-    check(core().tq_embed(ptr(tokens), ptr(table), dtype_code(table), ptr(out), T, H, V, ptr(status), stream()),
-          "embed")
+    check(core().tq_embed_scaled(ptr(tokens), ptr(table), dtype_code(table), ptr(out), T, H, V, ptr(status),
+                                 float(scale), stream()), "embed")
     return out
 
 
@@ -132,10 +133,14 @@ def embed_sinusoid(tokens: torch.Tensor, positions: torch.Tensor, table: torch.T
     return out
 
 
+GATE_SIGMOID, GATE_SILU, GATE_SILU_FIRST = 0, 1, 2
+
+
 def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *, groups: int = 1,
-                  gate: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None):
+                  gate: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                  gate_mode: int = GATE_SIGMOID):
     """RMS norm in `groups` consecutive groups of a row, times `weight`, optionally times sigmoid(gate) entry by
-    entry.  x float32 [*, W] and gate float32 [*, W] may be column slices of wider buffers (row strides are
+    entry (`gate_mode` GATE_SILU: times silu(gate) instead; GATE_SILU_FIRST: x times silu(gate) BEFORE the norm).  x float32 [*, W] and gate float32 [*, W] may be column slices of wider buffers (row strides are
     passed on); weight float32 [W]; out float32 or bfloat16 [R, W]."""
     W = x.shape[-1]
     R = out.shape[0]
@@ -153,7 +158,7 @@ def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.
     need_contiguous(weight=weight, rows=rows)
     check(core().tq_group_rmsnorm(ptr(x), x.stride(0), ptr(weight), ptr(gate), 0 if gate is None else gate.stride(0),
                                   ptr(out), dtype_code(out), out.stride(0), ptr(rows), R, W, groups, float(eps),
-                                  stream()), "group_rmsnorm")
+                                  int(gate_mode), stream()), "group_rmsnorm")
     return out
 
 
@@ -175,6 +180,15 @@ def add_normed(acc: torch.Tensor, sources, eps: float, scale: float):
         raise KernelError("add_normed: acc must be float32")
     need_contiguous(acc=acc)
     check(core().tq_add_normed(ptr(acc), *flat, len(sources), T, W, float(eps), float(scale), stream()), "add_normed")
+    return acc
+
+
+def add_scaled(acc: torch.Tensor, x: torch.Tensor, scale: float):
+    """acc += scale * x, both float32 and contiguous."""
+    if acc.dtype != torch.float32 or x.dtype != torch.float32 or acc.shape != x.shape:
+        raise KernelError("add_scaled: acc and x must be float32 of one shape")
+    need_contiguous(acc=acc, x=x)
+    check(core().tq_add_scaled(ptr(acc), ptr(x), acc.numel(), float(scale), stream()), "add_scaled")
     return acc
 
 

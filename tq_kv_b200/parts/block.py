@@ -49,3 +49,36 @@ class PrenormResidualBlock:
         if getattr(consumer, "takes_pending_norm", False) and getattr(norm, "pending", None) is not None:
             return norm.pending(h, act)
         return norm.forward(h, act)
+
+
+class ParallelResidualBlock:
+    """h += mult * (mixer(n) + feed_forward(n)) with ONE norm n = norm(h): both sublayers read the same normed
+    rows, their results are added in float32 and enter the residual stream times `residual_mult` (a block
+    parameter, 1 by default).  A layer may name no feed-forward."""
+    padded_rows_ok = True               # as far as its parts are
+
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.mult = float(spec.block_params.get("residual_mult", 1.0))
+        self.mixer_norm = make_part(spec.part("mixer_norm"))
+        self.mixer = make_part(spec.part("mixer"))
+        self.feed_forward = make_part(spec.part("feed_forward")) if spec.feed_forward is not None else None
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward) if p is not None]
+
+    def forward(self, h, ctx: StepContext) -> None:
+        x = self.mixer_norm.forward(h, ctx.runtime.act_dtype)       # run once: two readers
+        kernels.mark("norms")
+        if self.mult == 1.0:
+            self.mixer.forward(x, ctx, h)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(x, ctx, h)
+            return
+        import torch
+        y = torch.zeros_like(h)                                     # the sublayers add their results into it
+        self.mixer.forward(x, ctx, y)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(x, ctx, y)
+        kernels.add_scaled(h, y, self.mult)
+        kernels.mark("norms")

@@ -27,6 +27,7 @@ class TokenEmbedding(Part):
         # sinusoidal positions added to the rows: column 2i gets sin(p * base^(-2i / width)), column 2i+1 its cosine
         self.sinusoid_base = self.params.get("sinusoid_base")
         self.wants_positions = self.sinusoid_base is not None
+        self.scale = float(self.params.get("scale", 1.0))      # the rows are multiplied by it
         self.table = None
         self.rate = None
         self.status = None
@@ -49,8 +50,10 @@ class TokenEmbedding(Part):
         if self.wants_positions:
             if positions is None:
                 raise kernels.KernelError("this embedding adds positions and was given none")
+            if self.scale != 1.0:
+                raise kernels.KernelError("an embedding that adds positions has no scale")
             return kernels.embed_sinusoid(tokens, positions, self.table, self.rate, out, self.status)
-        return kernels.embed(tokens, self.table, out, self.status)
+        return kernels.embed(tokens, self.table, out, self.status, self.scale)
 
 
 class LMHead(Part):

@@ -1,0 +1,141 @@
+"""Softmax attention whose keys and values come from a small latent per token.
+
+With H heads, per head `dim` unrotated and `rot_dim` rotated query/key entries
+and values of `value_dim`, and a latent of `kv_rank`:
+
+    c_q = rms_norm(W_dq x) * w_q            q[h] = (W_uq c_q)[h] = [q_flat[h] (dim), q_rot[h] (rot_dim)]
+    [c' , k_r'] = W_dkv x                   c = rms_norm(c') * w_kv,  k_r = rotate(k_r')   (shared by the heads)
+    key[h] = [U_k[h] c, k_r]                value[h] = U_v[h] c
+    score = (q_flat[h] . U_k[h] c + rotate(q_rot[h]) . k_r) * scale,   softmax over the keys j <= i
+    out = W_o ((heads side by side) * sigmoid(W_g x))            (the gate is optional)
+
+Only c and k_r are cached: one row of kv_rank + rot_dim values per token (one key/value "head" whose value rows
+are not used).  The attention itself runs in the latent's space: the query is carried there,
+q~[h] = [U_k[h]^T q_flat[h], rotate(q_rot[h])], the attention kernels see one shared key/value head whose value
+is the cached row itself, and the weighted mean of latents is expanded afterwards, U_v[h] mean(c)
+(csrc/latent_attention.cu).  Prompts from position 0 attend over the step's own rows, everything else reads the
+pages.  Rows are padded with zeros to a multiple of 16 values (what the attention kernels take).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache import KVRequest
+from ..config import ConfigError
+from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
+from .registry import make_part
+
+MAX_ROW = 256          # widest cached row (latent + rotated part) the attention kernels take
+
+
+class LatentAttention(Mixer):
+    padded_rows_ok = True               # causal, and rows past a sequence's new length are not cached
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.dim, self.rot_dim = int(p["heads"]), int(p["dim"]), int(p["rot_dim"])
+        self.value_dim = int(p["value_dim"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        self.output_gate = bool(p.get("output_gate", False))
+        self.names = dict(p["names"])
+        self.position = make_part(p["position"])
+        self.row = -(-(self.kv_rank + self.rot_dim) // 16) * 16
+        if self.row > MAX_ROW:
+            raise ConfigError(f"latent attention: a cached row of {self.kv_rank} + {self.rot_dim} values exceeds the "
+                              f"attention kernels' {MAX_ROW}")
+        if self.position.rotary_dim > self.rot_dim:
+            raise ConfigError("latent attention: more rotated entries than the rotated part holds")
+        self.w_in = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.q_norm_w = self.kv_norm_w = None
+
+    def _n(self, which: str) -> str:
+        return self.prefix + self.names[which]
+
+    def weight_specs(self):
+        h, H = self.hidden, self.heads
+        specs = [WeightSpec(self._n("q_down"), (self.q_rank, h), "matrix"),
+                 WeightSpec(self._n("q_norm"), (self.q_rank,), "norm_scale"),
+                 WeightSpec(self._n("q_up"), (H * (self.dim + self.rot_dim), self.q_rank), "matrix"),
+                 WeightSpec(self._n("kv_down"), (self.kv_rank + self.rot_dim, h), "matrix"),
+                 WeightSpec(self._n("kv_norm"), (self.kv_rank,), "norm_scale"),
+                 WeightSpec(self._n("k_up"), (H * self.dim, self.kv_rank), "matrix"),
+                 WeightSpec(self._n("v_up"), (H * self.value_dim, self.kv_rank), "matrix"),
+                 WeightSpec(self._n("out"), (h, H * self.value_dim), "matrix")]
+        if self.output_gate:
+            specs.append(WeightSpec(self._n("gate"), (H * self.value_dim, h), "matrix"))
+        return specs
+
+    def bind(self, tensors, runtime: Runtime, shared=None):
+        ws = [tensors[self._n("q_down")], tensors[self._n("kv_down")]]
+        if self.output_gate:
+            ws.append(tensors[self._n("gate")])
+        if len({w.dtype for w in ws}) != 1:
+            ws = [w.to(torch.float32) for w in ws]
+        self.w_in = torch.cat(ws, dim=0).contiguous()          # query latent | key/value latent, rotated part | gate
+        self.w_uq = tensors[self._n("q_up")].contiguous()
+        act = runtime.act_dtype                                 # the per-head products read these in the activations' dtype
+        self.w_uk = tensors[self._n("k_up")].to(act).contiguous()
+        self.w_uv = tensors[self._n("v_up")].to(act).contiguous()
+        self.w_o = tensors[self._n("out")].contiguous()
+        self.q_norm_w = float32_vector(tensors[self._n("q_norm")])
+        self.kv_norm_w = float32_vector(tensors[self._n("kv_norm")])
+        self.position.bind(tensors, runtime, shared)
+        self.position.prepare(runtime, shared)
+
+    def cache_request(self):
+        return KVRequest(1, self.row, None, 1)
+
+    @staticmethod
+    def _use_packed(start_pos, step_lens, owns_cache) -> bool:
+        return owns_cache and all(s == 0 for s in start_pos) and any(n > 1 for n in step_lens)
+
+    def forward(self, x, ctx: StepContext, residual):
+        b, kv, dev = ctx.batch, ctx.kv, residual.device
+        act = ctx.runtime.act_dtype
+        H, row, pos = self.heads, self.row, self.position
+        proj = kernels.linear(x, self.w_in, out_dtype=torch.float32)
+        kernels.mark("qkv")
+        T = proj.shape[0]
+        owns = kv is not None and kv.writes
+        packed = self._use_packed(b.host_start, b.host_lens, owns)
+        cq = torch.empty((T, self.q_rank), dtype=act, device=dev)
+        rows = torch.empty((T, row), dtype=act, device=dev) if packed else None
+        rot = dict(cos=pos.cos, sin=pos.sin, rot_dims=pos.rotary_dim, paired=pos.paired, tok_pos=b.tok_pos)
+        kernels.latent_rows(proj, cq, off_q=0, off_kv=self.q_rank, q_rank=self.q_rank, kv_rank=self.kv_rank,
+                            rot_dim=self.rot_dim, row_width=row, q_weight=self.q_norm_w, kv_weight=self.kv_norm_w,
+                            eps=self.eps, tok_seq=b.tok_seq, new_lens=b.new_lens, row_out=rows,
+                            pages=kv.k_pages if owns else None, block_table=kv.block_table if owns else None,
+                            table_width=kv.table_width if owns else 0,
+                            page_tokens=kv.page_tokens if kv is not None else 64, **rot)
+        kernels.mark("rotary")
+        q = kernels.linear(cq, self.w_uq, out_dtype=torch.float32)
+        kernels.mark("qkv")
+        qa = torch.empty((T, H * row), dtype=act, device=dev)
+        kernels.latent_query(q, self.w_uk, qa, heads=H, dim=self.dim, rot_dim=self.rot_dim, kv_rank=self.kv_rank,
+                             row_width=row, **rot)
+        kernels.mark("rotary")
+        lat = torch.empty_like(qa)
+        common = dict(n_heads=H, n_kv_heads=1, head_dim=row, tok_pos=b.tok_pos, tok_seq=b.tok_seq,
+                      cu_seqlens=b.cu_seqlens, start_pos=b.start_pos, window=None, scale=self.scale)
+        if packed:
+            kernels.attention(qa, lat, k_packed=rows, v_packed=rows, **common)
+        else:
+            n_splits = kernels.plan_splits(T, 1, b.max_new_len, ctx.runtime.sm_count)
+            scratch = None
+            if n_splits > 1:
+                scratch = torch.empty(kernels.split_scratch_floats(T, H, row, n_splits), dtype=torch.float32, device=dev)
+            kernels.attention(qa, lat, k_pages=kv.k_pages, v_pages=kv.k_pages, block_table=kv.block_table,
+                              table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
+                              n_splits=n_splits, scratch=scratch, **common)
+        kernels.mark("attention")
+        y = torch.empty((T, H * self.value_dim), dtype=act, device=dev)
+        gate = proj[:, self.q_rank + self.kv_rank + self.rot_dim:] if self.output_gate else None
+        kernels.latent_expand(lat, self.w_uv, y, heads=H, kv_rank=self.kv_rank, row_width=row,
+                              value_dim=self.value_dim, gate=gate)
+        kernels.mark("rotary")
+        kernels.linear(y, self.w_o, out=residual, accumulate=True)
+        kernels.mark("o")

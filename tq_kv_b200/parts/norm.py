@@ -1,5 +1,7 @@
 """RMS norm.  Reference: src/models/turbo_generic.rs:41-51 — computed in
-float32: x / sqrt(mean(x^2) + eps) * weight; no bias, no `1 + weight`."""
+float32: x / sqrt(mean(x^2) + eps) * weight; no bias, no `1 + weight`.  A model that stores its norm weights as
+the distance from one says so with `weight_offset` (1.0): the offset is added once, in float32, when the
+weights are bound."""
 from __future__ import annotations
 
 from typing import Optional
@@ -19,6 +21,7 @@ class RMSNorm(Norm):
         self.width = int(self.params["width"])
         self.eps = float(self.params["eps"])
         self.weight_name = self.params.get("weight_name") or self.prefix + "weight"
+        self.weight_offset = float(self.params.get("weight_offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self):
@@ -26,6 +29,8 @@ class RMSNorm(Norm):
 
     def bind(self, tensors, runtime: Runtime, shared=None):
         self.weight = float32_vector(tensors[self.weight_name])
+        if self.weight_offset != 0.0:
+            self.weight = (self.weight + self.weight_offset).contiguous()
 
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]

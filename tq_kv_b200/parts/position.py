@@ -63,3 +63,42 @@ class RotaryHalved(PositionEncoding):
             k_pages=kv.k_pages if write else None, v_pages=kv.v_pages if write else None,
             block_table=table, table_width=width, ring_pages=kv.ring_pages if write else 0,
             page_tokens=kv.page_tokens if kv is not None else 64, clear_input=clear_input)
+
+
+class RotaryTables(PositionEncoding):
+    """Cosines and sines of the angles pos * theta^(-2i / rotary_dim), i < rotary_dim / 2, for mixers whose own
+    kernels turn their vectors (`layout` says how the mixer pairs entries: "pairs" turns entry 2i with 2i + 1,
+    "halves" entry i with i + rotary_dim / 2).  The angles are formed in float64 on the host and their cosines
+    and sines rounded once to float32, so that the tables carry no error that grows with the position."""
+    padded_rows_ok = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.rotary_dim = int(self.params["rotary_dim"])
+        self.theta = float(self.params["theta"])
+        self.layout = self.params.get("layout", "pairs")
+        if self.layout not in ("pairs", "halves") or self.rotary_dim % 2:
+            raise ValueError(f"rotary tables: layout '{self.layout}' (pairs or halves), an even rotary_dim")
+        self.cos: Optional[torch.Tensor] = None
+        self.sin: Optional[torch.Tensor] = None
+
+    @property
+    def paired(self) -> bool:
+        return self.layout == "pairs"
+
+    def prepare(self, runtime: Runtime, shared: Optional[dict] = None) -> None:
+        key = (("rotary_tables", self.rotary_dim, self.theta), runtime.max_context, str(runtime.device))
+        if shared is not None and key in shared:
+            self.cos, self.sin = shared[key]
+            return
+        half = max(1, self.rotary_dim // 2)
+        i = torch.arange(half, dtype=torch.float64)
+        rate = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(2, self.rotary_dim))
+        ang = torch.arange(runtime.max_context, dtype=torch.float64).reshape(-1, 1) * rate.reshape(1, -1)
+        self.cos = torch.cos(ang).to(torch.float32).contiguous().to(runtime.device)
+        self.sin = torch.sin(ang).to(torch.float32).contiguous().to(runtime.device)
+        if shared is not None:
+            shared[key] = (self.cos, self.sin)
+
+    def encode_and_store(self, *args, **kwargs):
+        raise NotImplementedError("rotary tables are applied by the mixer's own kernels")
