@@ -712,7 +712,7 @@ def test_sizes_outside_the_kernels_reach_are_refused():
     with pytest.raises(kernels.KernelError, match="head_dim"):
         kernels.check_head_geometry(4, 2, 24)
     with pytest.raises(kernels.KernelError, match="head_dim"):
-        kernels.check_head_geometry(4, 2, 272)
+        kernels.check_head_geometry(4, 2, 528)          # the general kernel takes rows of up to 512 values
     with pytest.raises(kernels.KernelError, match="shared"):
         kernels.check_head_geometry(5, 2, 64)
     with pytest.raises(kernels.KernelError, match="CUDA"):

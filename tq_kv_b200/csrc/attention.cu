@@ -10,7 +10,7 @@
 // reference) lets the query at position p see keys max(0, p-window+1) .. p.
 #include "common.cuh"
 
-#define ATT_MAX_PAIRS 4   // head_dim <= 256: each lane owns up to 4 pairs of dims
+#define ATT_MAX_PAIRS 8   // head_dim <= 512: each lane owns up to 8 pairs of dims
 
 struct KVSource {
     // packed: rows of this step, [T, nkv, hd]; key at position j of row b is token cu[b] + j - start[b]

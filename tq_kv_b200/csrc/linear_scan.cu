@@ -189,9 +189,11 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
                     cp_async16(row + 4 * DP, a.w + t * a.ldw + head * d + i);
                 }
             }
-            for (int idx = tid; idx < n * c4; idx += THREADS) {
-                const int tt = idx / c4, c = (idx - tt * c4) * 4;
-                cp_async16(dv + tt * CT + c, a.v + (size_t)(base + tt) * a.ldp + head * e + col0 + c);
+            if (CT % 4 == 0) {                 // (a block of fewer than four columns takes its values one by one, below)
+                for (int idx = tid; idx < n * c4; idx += THREADS) {
+                    const int tt = idx / c4, c = (idx - tt * c4) * 4;
+                    cp_async16(dv + tt * CT + c, a.v + (size_t)(base + tt) * a.ldp + head * e + col0 + c);
+                }
             }
         } else {
             for (int idx = tid; idx < n * d; idx += THREADS) {
@@ -206,6 +208,8 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
                     row[4 * DP] = a.w[t * a.ldw + head * d + i];
                 }
             }
+        }
+        if (!a.vec || CT % 4 != 0) {
             for (int idx = tid; idx < n * cols; idx += THREADS) {
                 const int tt = idx / cols, c = idx - tt * cols;
                 dv[tt * CT + c] = a.v[(size_t)(base + tt) * a.ldp + head * e + col0 + c];

@@ -146,7 +146,7 @@ TQ_API int tq_short_conv(const float* x, int ldx, const float* w, const float* b
                          const float* scales, float unit_eps, const float* gate_raw, int ldg, const float* beta_raw,
                          int ldb, const float* A_log, const float* dt_bias, float* scal, int H, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
-    if (!x || !w || !out || !state || !tok_seq || !cu_seqlens || !slots || C <= 0 || K < 1 || K > CONV_MAX_TAPS ||
+    if (!x || !w || !out || (!state && K > 1) || !tok_seq || !cu_seqlens || !slots || C <= 0 || K < 1 || K > CONV_MAX_TAPS ||
         n_reg < 1 || n_reg > CONV_MAX_REGIONS || !regions || !scales || state_stride < (long long)(K - 1) * C)
         return (int)cudaErrorInvalidValue;
     if (single && n_tokens != n_seqs) return (int)cudaErrorInvalidValue;

@@ -8,7 +8,7 @@ import torch
 
 from ._lib import KernelError, check, core, dtype_code, need_contiguous, ptr, stream, tc_status_word
 
-MAX_HEAD_DIM = 256
+MAX_HEAD_DIM = 512    # of the general kernel; the Qwen2 configuration keeps its own limit of 256
 NOT_SUPPORTED = 801     # cudaErrorNotSupported: a specialised kernel declines the shape
 USE_TC_ATTENTION = True  # prompts: the tcgen05 kernel (csrc/flash_prefill_tc.cu) before the mma.sync one
 

@@ -23,10 +23,11 @@ import torch
 from .. import kernels
 from ..cache import KVRequest
 from ..config import ConfigError
+from ..kernels.attention import MAX_HEAD_DIM
 from .base import Mixer, Runtime, StepContext, WeightSpec, float32_vector
 from .registry import make_part
 
-MAX_ROW = 256          # widest cached row (latent + rotated part) the attention kernels take
+MAX_ROW = MAX_HEAD_DIM          # widest cached row (latent + rotated part) the attention kernels take
 
 
 class LatentAttention(Mixer):

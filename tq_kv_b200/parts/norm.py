@@ -25,7 +25,8 @@ class RMSNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self):
-        return [WeightSpec(self.weight_name, (self.width,), "norm_scale")]
+        # (stored as the distance from one: random weights are then drawn around zero)
+        return [WeightSpec(self.weight_name, (self.width,), "norm_offset" if self.weight_offset else "norm_scale")]
 
     def bind(self, tensors, runtime: Runtime, shared=None):
         self.weight = float32_vector(tensors[self.weight_name])

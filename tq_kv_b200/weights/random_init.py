@@ -2,7 +2,7 @@
 a model folder (config.json + model.safetensors) that the loader reads back.
 
 Init rules by role: matrices and embeddings N(0, 0.02^2); biases N(0, 0.02^2);
-norm scales 1 + N(0, 0.1^2); the taps of short convolutions N(0, 0.3^2).  The generator is counter-based: element i of a
+norm scales 1 + N(0, 0.1^2) (N(0, 0.1^2) where the model adds the one itself); the taps of short convolutions N(0, 0.3^2).  The generator is counter-based: element i of a
 tensor depends on (seed, tensor name, i) only, so a tensor's values depend
 neither on which other tensors exist nor on where they are made.  The host
 twin below (numpy) and the device kernel (csrc/random_fill.cu) do the same
@@ -23,7 +23,7 @@ import torch
 
 from .safetensors_io import write_safetensors
 
-_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02, "norm_scale": 0.1, "conv": 0.3}
+_STD = {"matrix": 0.02, "embedding": 0.02, "bias": 0.02, "norm_scale": 0.1, "norm_offset": 0.1, "conv": 0.3}
 _OFFSET = {"norm_scale": 1.0}
 _MASK = (1 << 64) - 1
 _CHUNK = 1 << 15          # elements generated at a time on the host (stays in the cache)
