@@ -315,3 +315,35 @@ def test_latent_rows_query_and_expansion(dtype, H, d, r, e, qr, n, dims, paired)
     _close(y, want_y * torch.sigmoid(gate[:, 1:1 + H * e].double().cpu()), tol, "expansion")
     kernels.latent_expand(lat, uv, y, heads=H, kv_rank=n, row_width=rp, value_dim=e)
     _close(y, want_y, tol, "expansion without a gate")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, d, r, e, n", [(3, 16, 8, 24, 48), (2, 8, 12, 40, 30), (4, 64, 64, 128, 96)])
+def test_expanded_heads_for_prompts(dtype, H, d, r, e, n):
+    from tq_kv_b200 import kernels
+    torch.manual_seed(e)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    T, rp, hw = 7, -(-(n + r) // 16) * 16, -(-max(d + r, e) // 16) * 16
+    pos_h = [0, 1, 2, 63, 64, 5, 130]
+    rate = torch.pow(torch.tensor(1e4, dtype=torch.float64), -2.0 * torch.arange(r // 2, dtype=torch.float64) / r)
+    ang = torch.arange(200, dtype=torch.float64).unsqueeze(1) * rate
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    q, kfv = torch.randn(T, H * (d + r), device=DEV), torch.randn(T, H * (d + e), device=DEV)
+    rows = torch.randn(T, rp, device=DEV).to(dtype)
+    qo, ko, vo = (torch.full((T, H * hw), 9.0, dtype=dtype, device=DEV) for _ in range(3))
+    kernels.latent_heads(q, kfv, rows, qo, ko, vo, heads=H, dim=d, rot_dim=r, value_dim=e, kv_rank=n, cos=cos, sin=sin,
+                         rot_dims=r, paired=True, tok_pos=_i32(pos_h))
+    q64 = q.double().cpu().reshape(T, H, d + r)
+    wq, wk, wv = (torch.zeros(T, H, hw, dtype=torch.float64) for _ in range(3))
+    wq[:, :, :d] = q64[:, :, :d]
+    wq[:, :, d:d + r] = pr.rotate_pairs(q64[:, :, d:], torch.tensor(pos_h), r, 1e4)
+    wk[:, :, :d] = kfv.double().cpu()[:, :H * d].reshape(T, H, d)
+    wk[:, :, d:d + r] = rows.double().cpu()[:, n:n + r].unsqueeze(1)
+    wv[:, :, :e] = kfv.double().cpu()[:, H * d:].reshape(T, H, e)
+    _close(qo, wq.reshape(T, -1), tol, "queries")
+    _close(ko, wk.reshape(T, -1), tol, "keys")
+    _close(vo, wv.reshape(T, -1), tol, "values")
+    gate = torch.randn(T, H * e, device=DEV)
+    y = torch.empty(T, H * e, dtype=dtype, device=DEV)
+    kernels.latent_expand(vo, None, y, heads=H, kv_rank=hw, row_width=hw, value_dim=e, gate=gate)
+    _close(y, wv[:, :, :e].reshape(T, -1) * torch.sigmoid(gate.double().cpu()), tol, "gated heads")

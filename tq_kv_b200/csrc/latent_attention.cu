@@ -15,6 +15,11 @@
 //   latent_query   per (token, head): q~ as above
 //   latent_expand  per (token, head): o[h] = U_v[h] mean(c), times sigmoid(gate) entry by entry
 //
+//   latent_heads   for prompts that bring all their keys along: per (token, head) the query [q_flat, rot(q_rot), 0 ...],
+//                  the expanded key [U_k[h] c, k_r, 0 ...] and the value [U_v[h] c, 0 ...], all `hw` wide, for the
+//                  ordinary attention kernels (whose heads then are this mixer's heads); latent_expand without a
+//                  matrix then only gates and narrows the result
+//
 // Rotation: of the r rotated entries the first `rot_dims` are turned by the angle pos * rate_i (tables of cosines and
 // sines per position come ready-made), in neighbouring pairs (2i, 2i+1) if `paired`, else entry i with i + rot_dims/2.
 // Norms, rotation and the per-head sums are float32.
@@ -106,6 +111,38 @@ __global__ void latent_query_kernel(const float* __restrict__ q, int H, int d, i
     }
 }
 
+// q float32 [T, H * (d + r)]; kfv float32 [T, ldk]: head h's flat key at column h * d, its value at off_v + h * e;
+// rows [T, rp]: the cache rows, whose entries n .. n + r - 1 are the rotated key part.
+template <typename T>
+__global__ void latent_heads_kernel(const float* __restrict__ q, const float* __restrict__ kfv, int ldk, int off_v,
+                                    const T* __restrict__ rows, int rp, int n, int H, int d, int r, int e, int hw,
+                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
+                                    int paired, const int* __restrict__ tok_pos, T* __restrict__ q_out,
+                                    T* __restrict__ k_out, T* __restrict__ v_out) {
+    extern __shared__ float sh[];          // [r] this head's rotated query part, raw
+    const int t = blockIdx.x, h = blockIdx.y;
+    pdl_wait();
+    pdl_launch();
+    const float* qr = q + ((size_t)t * H + h) * (d + r);
+    for (int i = threadIdx.x; i < r; i += blockDim.x) sh[i] = qr[d + i];
+    __syncthreads();
+    const int pos = tok_pos[t];
+    const float* cs = cos_t + (size_t)pos * (rot_dims >> 1);
+    const float* sn = sin_t + (size_t)pos * (rot_dims >> 1);
+    const size_t o = ((size_t)t * H + h) * hw;
+    const float* kr = kfv + (size_t)t * ldk + (size_t)h * d;
+    const float* vr = kfv + (size_t)t * ldk + off_v + (size_t)h * e;
+    const T* rr = rows + (size_t)t * rp + n;
+    for (int i = threadIdx.x; i < hw; i += blockDim.x) {
+        T qv = from_f32<T>(0.f), kv = qv;
+        if (i < d) { qv = from_f32<T>(qr[i]); kv = from_f32<T>(kr[i]); }
+        else if (i < d + r) { qv = from_f32<T>(rot_entry(sh, i - d, rot_dims, paired, cs, sn)); kv = rr[i - d]; }
+        q_out[o + i] = qv;
+        k_out[o + i] = kv;
+        v_out[o + i] = i < e ? from_f32<T>(vr[i]) : from_f32<T>(0.f);
+    }
+}
+
 template <typename T>
 __global__ void latent_expand_kernel(const T* __restrict__ lat, int H, int n, int rp, int e, const T* __restrict__ uv,
                                      const float* __restrict__ gate, int ldg, T* __restrict__ out) {
@@ -117,6 +154,15 @@ __global__ void latent_expand_kernel(const T* __restrict__ lat, int H, int n, in
     const T* lr = lat + ((size_t)t * H + h) * rp;
     for (int i = threadIdx.x; i < n; i += blockDim.x) sh[i] = to_f32<T>(lr[i]);
     __syncthreads();
+    if (!uv) {                             // nothing to expand: the head's first e entries, gated
+        for (int j = threadIdx.x; j < e; j += blockDim.x) {
+            const size_t c = (size_t)h * e + j;
+            float acc = sh[j];
+            if (gate) acc *= 1.f / (1.f + expf(-gate[(size_t)t * ldg + c]));
+            out[(size_t)t * H * e + c] = from_f32<T>(acc);
+        }
+        return;
+    }
     for (int j = warp; j < e; j += n_warps) {
         const T* w = uv + ((size_t)h * e + j) * n;
         float acc = 0.f;
@@ -176,7 +222,7 @@ TQ_API int tq_latent_query(const float* q, int H, int d, int r, int n, int rp, c
 TQ_API int tq_latent_expand(const void* lat, int H, int n, int rp, int e, const void* uv, const float* gate, int ldg,
                             void* out, int dtype, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (!lat || !uv || !out || H <= 0 || H > 65535 || n <= 0 || rp < n || e <= 0) return (int)cudaErrorInvalidValue;
+    if (!lat || !out || H <= 0 || H > 65535 || n <= 0 || rp < n || e <= 0 || (!uv && e > n)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)n * sizeof(float);
     const dim3 grid(n_tokens, H);
     if (dtype == TQ_F32)
@@ -185,5 +231,26 @@ TQ_API int tq_latent_expand(const void* lat, int H, int n, int rp, int e, const 
     if (dtype == TQ_BF16)
         return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_expand_kernel<bf16>, grid, dim3(128), smem, stream,
                              (const bf16*)lat, H, n, rp, e, (const bf16*)uv, gate, ldg, (bf16*)out);
+    return (int)cudaErrorInvalidValue;
+}
+
+TQ_API int tq_latent_heads(const float* q, const float* kfv, int ldk, int off_v, const void* rows, int rp, int n, int H,
+                           int d, int r, int e, int hw, const float* cos_t, const float* sin_t, int rot_dims, int paired,
+                           const int* tok_pos, void* q_out, void* k_out, void* v_out, int dtype, int n_tokens,
+                           cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!q || !kfv || !rows || !cos_t || !sin_t || !tok_pos || !q_out || !k_out || !v_out || H <= 0 || H > 65535 ||
+        d <= 0 || r < 0 || e <= 0 || hw < d + r || hw < e || rp < n + r || rot_dims < 0 || rot_dims > r || (rot_dims & 1))
+        return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_tokens, H);
+    const size_t smem = (size_t)(r > 0 ? r : 1) * sizeof(float);
+    if (dtype == TQ_F32)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<float>, grid, dim3(128), smem, stream, q, kfv, ldk,
+                             off_v, (const float*)rows, rp, n, H, d, r, e, hw, cos_t, sin_t, rot_dims, paired, tok_pos,
+                             (float*)q_out, (float*)k_out, (float*)v_out);
+    if (dtype == TQ_BF16)
+        return tq_launch_pdl(TQ_PDL_ELEMENTWISE, latent_heads_kernel<bf16>, grid, dim3(128), smem, stream, q, kfv, ldk,
+                             off_v, (const bf16*)rows, rp, n, H, d, r, e, hw, cos_t, sin_t, rot_dims, paired, tok_pos,
+                             (bf16*)q_out, (bf16*)k_out, (bf16*)v_out);
     return (int)cudaErrorInvalidValue;
 }

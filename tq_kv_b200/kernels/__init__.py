@@ -6,12 +6,12 @@ from .elementwise import (GATE_SIGMOID, GATE_SILU, GATE_SILU_FIRST, add_into, ad
                           scale_inplace, select_tokens, swiglu, tanh_rows)
 from .gemm import (PendingNorm, check_tc_status, decode_gemm_tc, gemm_tc, gemm_tiled, gemv_rows, linear, product_adds_shares, set_gemm_tc_mode,
                    skinny_gemm)
-from .latent import latent_expand, latent_query, latent_rows
+from .latent import latent_expand, latent_heads, latent_query, latent_rows
 from .scan import gated_scan, linear_scan, short_conv
 from .sampling import sample
 from .sigmoid import rownorm_qkv_store, sigmoid_attention
 
 __all__ = ["KernelError", "PendingNorm", "Timeline", "mark", "add_into", "attention", "check_head_geometry", "check_tc_status", "decode_gemm_tc", "embed", "launches", "mark_tc_launched", "gemm_tc", "gemm_tiled", "set_gemm_tc_mode", "gemv_rows",
-           "GATE_SIGMOID", "GATE_SILU", "GATE_SILU_FIRST", "add_scaled", "gated_scan", "latent_expand", "latent_query", "latent_rows", "short_conv",
+           "GATE_SIGMOID", "GATE_SILU", "GATE_SILU_FIRST", "add_scaled", "gated_scan", "latent_expand", "latent_heads", "latent_query", "latent_rows", "short_conv",
            "add_normed", "embed_sinusoid", "group_rmsnorm", "linear_scan", "rownorm_qkv_store", "scale_inplace", "sigmoid_attention", "tanh_rows",
            "linear", "plan_splits", "product_adds_shares", "qkv_rope_cache", "random_fill", "rmsnorm", "select_tokens", "sample", "skinny_gemm", "split_scratch_floats", "swiglu"]

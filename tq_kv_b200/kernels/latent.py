@@ -67,22 +67,52 @@ def latent_query(q: torch.Tensor, up_k: torch.Tensor, out: torch.Tensor, *, head
     return out
 
 
-def latent_expand(lat: torch.Tensor, up_v: torch.Tensor, out: torch.Tensor, *, heads: int, kv_rank: int,
+def latent_heads(q: torch.Tensor, kfv: torch.Tensor, rows: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
+                 v_out: torch.Tensor, *, heads: int, dim: int, rot_dim: int, value_dim: int, kv_rank: int, cos, sin,
+                 rot_dims: int, paired: bool, tok_pos):
+    """Expanded heads for the ordinary attention kernels, all `hw` = q_out.shape[1] / heads wide: q_out[t, h] =
+    [q[t, h, :dim], rotate(q[t, h, dim:]), zeros], k_out[t, h] = [flat key of head h, rows[t, kv_rank : kv_rank +
+    rot_dim], zeros], v_out[t, h] = [value of head h, zeros].  q float32 [T, heads * (dim + rot_dim)]; kfv float32
+    [T, heads * dim + heads * value_dim] (flat keys, then values, head by head); rows [T, row] of the outputs'
+    dtype (the cache rows)."""
+    T = q.shape[0]
+    hw = q_out.shape[1] // heads
+    if q.dtype != torch.float32 or tuple(q.shape) != (T, heads * (dim + rot_dim)):
+        raise KernelError("latent_heads: q must be float32 [T, heads * (dim + rot_dim)]")
+    if kfv.dtype != torch.float32 or tuple(kfv.shape) != (T, heads * (dim + value_dim)) or kfv.stride(1) != 1:
+        raise KernelError("latent_heads: kfv must be float32 [T, heads * dim + heads * value_dim]")
+    if hw < max(dim + rot_dim, value_dim) or rows.shape[0] != T or rows.shape[1] < kv_rank + rot_dim:
+        raise KernelError("latent_heads: heads too narrow, or rows without the rotated part")
+    for t in (q_out, k_out, v_out):
+        if tuple(t.shape) != (T, heads * hw) or t.dtype != rows.dtype:
+            raise KernelError("latent_heads: q_out, k_out, v_out must be [T, heads * hw] of rows' dtype")
+    _check_tables(cos, sin, rot_dims, rot_dim)
+    need_contiguous(q=q, rows=rows, q_out=q_out, k_out=k_out, v_out=v_out, cos=cos, sin=sin)
+    check(core().tq_latent_heads(ptr(q), ptr(kfv), kfv.stride(0), heads * dim, ptr(rows), rows.shape[1], kv_rank, heads,
+                                 dim, rot_dim, value_dim, hw, ptr(cos), ptr(sin), rot_dims, int(paired), ptr(tok_pos),
+                                 ptr(q_out), ptr(k_out), ptr(v_out), dtype_code(q_out), T, stream()), "latent_heads")
+
+
+def latent_expand(lat: torch.Tensor, up_v: Optional[torch.Tensor], out: torch.Tensor, *, heads: int, kv_rank: int,
                   row_width: int, value_dim: int, gate: Optional[torch.Tensor] = None):
     """out[t, h] = up_v[h] lat[t, h, :kv_rank], times sigmoid(gate[t, h]) entry by entry.  lat [T, heads *
     row_width]; up_v [heads * value_dim, kv_rank]; gate float32 [T, heads * value_dim] (may be a column slice);
-    out [T, heads * value_dim]."""
+    out [T, heads * value_dim].  Without up_v (then kv_rank >= value_dim) a head's first value_dim entries pass,
+    gated."""
     T = lat.shape[0]
     if tuple(lat.shape) != (T, heads * row_width) or tuple(out.shape) != (T, heads * value_dim) or lat.dtype != out.dtype:
         raise KernelError("latent_expand: lat must be [T, heads * row_width] and out [T, heads * value_dim] of one dtype")
-    if tuple(up_v.shape) != (heads * value_dim, kv_rank) or up_v.dtype != out.dtype:
+    if up_v is None:
+        if kv_rank < value_dim:
+            raise KernelError("latent_expand: without a matrix the heads must hold value_dim entries")
+    elif tuple(up_v.shape) != (heads * value_dim, kv_rank) or up_v.dtype != out.dtype:
         raise KernelError("latent_expand: up_v must be [heads * value_dim, kv_rank] of out's dtype")
     ldg = 0
     if gate is not None:
         if gate.dtype != torch.float32 or tuple(gate.shape) != (T, heads * value_dim) or gate.stride(1) != 1:
             raise KernelError("latent_expand: gate must be float32 [T, heads * value_dim]")
         ldg = gate.stride(0)
-    need_contiguous(lat=lat, up_v=up_v, out=out)
+    need_contiguous(lat=lat, up_v=up_v, out=out)        # (need_contiguous passes None)
     check(core().tq_latent_expand(ptr(lat), heads, kv_rank, row_width, value_dim, ptr(up_v), ptr(gate), ldg, ptr(out),
                                   dtype_code(out), T, stream()), "latent_expand")
     return out

@@ -13,8 +13,11 @@ Only c and k_r are cached: one row of kv_rank + rot_dim values per token (one ke
 are not used).  The attention itself runs in the latent's space: the query is carried there,
 q~[h] = [U_k[h]^T q_flat[h], rotate(q_rot[h])], the attention kernels see one shared key/value head whose value
 is the cached row itself, and the weighted mean of latents is expanded afterwards, U_v[h] mean(c)
-(csrc/latent_attention.cu).  Prompts from position 0 attend over the step's own rows, everything else reads the
-pages.  Rows are padded with zeros to a multiple of 16 values (what the attention kernels take).
+(csrc/latent_attention.cu).  That is how everything that reads the pages runs (decoding, portions of prompts, a
+prompt beside decoding rows).  Prompts from position 0 bring all their keys along: there the keys and values of all
+heads are expanded once, by two matrix products, and the ordinary attention kernels run with this mixer's heads
+(fewer operations per score, and the tensor-core prompt kernels take the heads' widths).  Rows are padded with
+zeros to a multiple of 16 values (what the attention kernels take).
 """
 from __future__ import annotations
 
@@ -81,6 +84,8 @@ class LatentAttention(Mixer):
         act = runtime.act_dtype                                 # the per-head products read these in the activations' dtype
         self.w_uk = tensors[self._n("k_up")].to(act).contiguous()
         self.w_uv = tensors[self._n("v_up")].to(act).contiguous()
+        self.w_ukv = torch.cat([self.w_uk, self.w_uv], dim=0).contiguous()     # prompts expand keys and values at once
+        self.head_width = -(-max(self.dim + self.rot_dim, self.value_dim) // 16) * 16
         self.w_o = tensors[self._n("out")].contiguous()
         self.q_norm_w = float32_vector(tensors[self._n("q_norm")])
         self.kv_norm_w = float32_vector(tensors[self._n("kv_norm")])
@@ -115,26 +120,43 @@ class LatentAttention(Mixer):
         kernels.mark("rotary")
         q = kernels.linear(cq, self.w_uq, out_dtype=torch.float32)
         kernels.mark("qkv")
+        gate = proj[:, self.q_rank + self.kv_rank + self.rot_dim:] if self.output_gate else None
+        y = torch.empty((T, H * self.value_dim), dtype=act, device=dev)
+        if packed:
+            # A prompt from position 0 brings all its keys along: they are expanded once (two matrix products for
+            # all heads) and the ordinary attention kernels run with this mixer's heads as they are.
+            hw = self.head_width
+            kfv = kernels.linear(rows[:, :self.kv_rank], self.w_ukv, out_dtype=torch.float32)
+            kernels.mark("qkv")
+            qh, kh, vh = (torch.empty((T, H * hw), dtype=act, device=dev) for _ in range(3))
+            kernels.latent_heads(q, kfv, rows, qh, kh, vh, heads=H, dim=self.dim, rot_dim=self.rot_dim,
+                                 value_dim=self.value_dim, kv_rank=self.kv_rank, **rot)
+            kernels.mark("rotary")
+            oh = torch.empty_like(qh)
+            kernels.attention(qh, oh, k_packed=kh, v_packed=vh, n_heads=H, n_kv_heads=H, head_dim=hw, tok_pos=b.tok_pos,
+                              tok_seq=b.tok_seq, cu_seqlens=b.cu_seqlens, start_pos=b.start_pos, window=None,
+                              scale=self.scale)
+            kernels.mark("attention")
+            kernels.latent_expand(oh, None, y, heads=H, kv_rank=hw, row_width=hw, value_dim=self.value_dim, gate=gate)
+            kernels.mark("rotary")
+            kernels.linear(y, self.w_o, out=residual, accumulate=True)
+            kernels.mark("o")
+            return
         qa = torch.empty((T, H * row), dtype=act, device=dev)
         kernels.latent_query(q, self.w_uk, qa, heads=H, dim=self.dim, rot_dim=self.rot_dim, kv_rank=self.kv_rank,
                              row_width=row, **rot)
         kernels.mark("rotary")
         lat = torch.empty_like(qa)
-        common = dict(n_heads=H, n_kv_heads=1, head_dim=row, tok_pos=b.tok_pos, tok_seq=b.tok_seq,
-                      cu_seqlens=b.cu_seqlens, start_pos=b.start_pos, window=None, scale=self.scale)
-        if packed:
-            kernels.attention(qa, lat, k_packed=rows, v_packed=rows, **common)
-        else:
-            n_splits = kernels.plan_splits(T, 1, b.max_new_len, ctx.runtime.sm_count)
-            scratch = None
-            if n_splits > 1:
-                scratch = torch.empty(kernels.split_scratch_floats(T, H, row, n_splits), dtype=torch.float32, device=dev)
-            kernels.attention(qa, lat, k_pages=kv.k_pages, v_pages=kv.k_pages, block_table=kv.block_table,
-                              table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
-                              n_splits=n_splits, scratch=scratch, **common)
+        n_splits = kernels.plan_splits(T, 1, b.max_new_len, ctx.runtime.sm_count)
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.empty(kernels.split_scratch_floats(T, H, row, n_splits), dtype=torch.float32, device=dev)
+        kernels.attention(qa, lat, n_heads=H, n_kv_heads=1, head_dim=row, tok_pos=b.tok_pos, tok_seq=b.tok_seq,
+                          cu_seqlens=b.cu_seqlens, start_pos=b.start_pos, window=None, scale=self.scale,
+                          k_pages=kv.k_pages, v_pages=kv.k_pages, block_table=kv.block_table,
+                          table_width=kv.table_width, ring_pages=kv.ring_pages, page_tokens=kv.page_tokens,
+                          n_splits=n_splits, scratch=scratch)
         kernels.mark("attention")
-        y = torch.empty((T, H * self.value_dim), dtype=act, device=dev)
-        gate = proj[:, self.q_rank + self.kv_rank + self.rot_dim:] if self.output_gate else None
         kernels.latent_expand(lat, self.w_uv, y, heads=H, kv_rank=self.kv_rank, row_width=row,
                               value_dim=self.value_dim, gate=gate)
         kernels.mark("rotary")
