@@ -26,10 +26,11 @@ then 256 decode steps.  Peaks come from MEASURED_PEAKS.json beside this file
 if it exists, else from an earlier measurement on the same kind of machine
 (6.65 TB/s, 1.59 PFLOP/s).
 
-`--design zodosun [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the Zodosun decoder beside the Qwen2
+`--design zodosun|rirudra [--sizes 1k,2k,4k] [--prompt 2048]` is another program: the named decoder beside the Qwen2
 decoder of the same width, depth, heads, feed-forward and vocabulary (random weights, bfloat16): device time of a
 prompt, of decode steps at batch 8 and 64, and the time by class of kernel with what the attention and scan
-kernels reach of their rooflines, as one JSON line of its own.  The default workload and its line are untouched.
+kernels reach of their rooflines, as one JSON line of its own (`--design rirudra` also runs the Zodosun decoder,
+whose scans are the like kernels of its own).  The default workload and its line are untouched.
 
 The reference arm (`--impl reference`) cannot run here: the reference is a
 Rust workspace and no Rust toolchain is installed, so it prints its
@@ -208,8 +209,64 @@ def design_configs(width: int, ff: int, layers: int, vocab: int) -> tuple[dict, 
     return zod, qwen
 
 
+def rirudra_config(width: int, ff: int, layers: int, vocab: int) -> dict:
+    """A Rirudra configuration of the given width: attention through a latent of 96 values and a rotated part of 32
+    (heads of 96 + 32 key and 128 value entries), a state-space layer with twice the width inside (heads of 64, a
+    state of 128), a gated delta rule with heads of 128 on half as many key heads; layers in that order, every
+    fourth again attention."""
+    heads = width // 128
+    mlp = {"kind": "dense", "ff": ff}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": 96, "rot_dim": 32, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": 96,
+        "scale": 128 ** -0.5, "rot": {"base": 1e6, "dims": 32}}}
+    ssm = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1,
+                                                    "norm_groups": 1, "conv": 4}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128,
+                                                    "vdim": 128, "conv": 4}}
+    order = [latent, ssm, delta, latent]
+    return {"architecture": "Rirudra", "vocab": vocab, "width": width, "embedding": {"scale": 8.0},
+            "residual_mult": 0.5, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "layers": [order[i % 4] for i in range(layers)]}
+
+
+def rirudra_roofline(rec: dict, pk: dict, P: int, sms: int) -> dict:
+    """What the attention and scan classes of the Rirudra decoder reach of their rooflines, beside the like classes
+    of the Qwen2 decoder (attention) and of the Zodosun decoder (scans)."""
+    width, layers = rec["width"], rec["layers"]
+    heads = width // 128
+    r, q, z = rec["rirudra"], rec["qwen2"], rec["zodosun"]
+    kinds = [("latent", "ssm", "delta", "latent")[i % 4] for i in range(layers)]
+    n_lat, n_ssm, n_delta = kinds.count("latent"), kinds.count("ssm"), kinds.count("delta")
+    fp32_tflops = 2 * FP32_FMA_PER_SM_PER_CLOCK * sms * 1900.0 * 1e6 / 1e12
+    roof = {"fp32_fma_tflops_nominal": round(fp32_tflops, 1)}
+    attn_flops = 4 * heads * 128 * P * (P + 1) / 2                      # per layer, heads of 128 either way
+    roof["rirudra.prefill.attention.frac_of_bf16"] = round(
+        attn_flops * n_lat / (r["prefill_classes_us"]["attention"] * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+    roof["qwen2.prefill.attention.frac_of_bf16"] = round(
+        attn_flops * layers / (q["prefill_classes_us"]["attention"] * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+    ssm_state, delta_state = (2 * width // 64) * 128 * 64, heads * 128 * 128          # floats per sequence and layer
+    scan_flops = P * (5 * ssm_state * n_ssm + 8 * delta_state * n_delta)
+    roof["rirudra.prefill.scan.frac_of_fp32_fma"] = round(
+        scan_flops / (r["prefill_classes_us"]["scan"] * 1e-6) / 1e12 / fp32_tflops, 3)
+    z_delta = sum(1 for i in range(layers) if i % 4 != 2)
+    roof["zodosun.prefill.scan.frac_of_fp32_fma"] = round(
+        P * heads * 128 * 128 * (8 * z_delta + 5 * (layers - z_delta)) / (z["prefill_classes_us"]["scan"] * 1e-6)
+        / 1e12 / fp32_tflops, 3)
+    roof["rirudra.decode_b64.scan.frac_of_hbm"] = round(
+        64 * (ssm_state * n_ssm + delta_state * n_delta) * 4 * 2 / (r["decode_b64_classes_us"]["scan"] * 1e-6) / 1e9
+        / pk["hbm_gbs"], 3)
+    roof["zodosun.decode_b64.scan.frac_of_hbm"] = round(
+        64 * heads * 128 * 128 * 4 * 2 * layers / (z["decode_b64_classes_us"]["scan"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+    kv_row = 2 * max(1, width // 512) * 128 * 2
+    roof["rirudra.decode_b64.attention.frac_of_hbm"] = round(
+        64 * (P + 16) * 128 * 2 * n_lat / (r["decode_b64_classes_us"]["attention"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+    roof["qwen2.decode_b64.attention.frac_of_hbm"] = round(
+        64 * (P + 16) * kv_row * layers / (q["decode_b64_classes_us"]["attention"] * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+    return roof
+
+
 def design_compare(args) -> int:
-    """Prefill and decode of the Zodosun decoder and of the Qwen2 decoder of equal size, random weights, bfloat16:
+    """Prefill and decode of the named decoder and of the Qwen2 decoder of equal size, random weights, bfloat16:
     device time of a 2,048-token prompt, of decode steps at batch 8 and 64 (replayed graphs), and the time by
     class of kernel with what each class reaches of its roofline."""
     import torch
@@ -220,13 +277,17 @@ def design_compare(args) -> int:
     gen = torch.Generator().manual_seed(0)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     P, ctx = args.prompt, args.prompt + 512
-    out = {"design": "zodosun", "beside": "qwen2", "dtype": "bf16", "data": "synthetic (random weights)",
+    out = {"design": args.design, "beside": "qwen2", "dtype": "bf16", "data": "synthetic (random weights)",
            "peaks": {**pk, "source": pk_src}, "prompt": P, "sizes": {}}
     with ClockSampler() as clocks:
         for name in args.sizes.split(","):
             width, ff, layers, vocab = DESIGN_SIZES[name]
             rec = out["sizes"][name] = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
-            for model, cfg in zip(("zodosun", "qwen2"), design_configs(width, ff, layers, vocab)):
+            zod, qwen = design_configs(width, ff, layers, vocab)
+            models = [("zodosun", zod), ("qwen2", qwen)]
+            if args.design == "rirudra":
+                models.insert(0, ("rirudra", rirudra_config(width, ff, layers, vocab)))
+            for model, cfg in models:
                 eng = tq.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_slots=64, max_context=ctx,
                                             max_tokens=64 * ctx)
                 r = rec[model] = {}
@@ -289,6 +350,9 @@ def design_compare(args) -> int:
                         eng.release(s)
                 del eng
                 torch.cuda.empty_cache()
+            if args.design == "rirudra":
+                rec["roofline"] = rirudra_roofline(rec, pk, P, sms)
+                continue
             # what the classes reach of their rooflines
             heads, d = width // 128, 128
             z, q = rec["zodosun"], rec["qwen2"]
@@ -321,7 +385,7 @@ def design_compare(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zodosun"],
+    ap.add_argument("--design", default=None, choices=["zodosun", "rirudra"],
                     help="instead of the default workload: this design beside the Qwen2 decoder of equal size")
     ap.add_argument("--sizes", default="1k,2k,4k", help="with --design: which of the sizes 1k, 2k, 4k (the model's width)")
     ap.add_argument("--gpus", type=int, default=1)

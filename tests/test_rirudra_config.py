@@ -26,7 +26,14 @@ def test_the_architecture_is_registered_and_a_configuration_round_trips():
             {"latent_attention": "latent_attention", "mamba2": "state_space_mixer", "delta": "gated_delta_mixer"}[x["type"]]
             for x in cfg["layers"]]
         assert [l.feed_forward is None for l in spec.layers] == [x["mlp"] is None for x in cfg["layers"]]
-        assert spec.head.params["tied_to"] == "embed" and spec.embedding.params["scale"] == cfg["embedding"]["scale"]
+        # the stream is kept divided by the residual factor: embeddings and the norms' eps carry it
+        m = cfg["residual_mult"]
+        assert spec.head.params["tied_to"] == "embed" and spec.embedding.params["scale"] == cfg["embedding"]["scale"] / m
+        assert spec.final_norm.params["eps"] == cfg["norm"]["eps"] / (m * m)
+        assert all(l.block_params["residual_mult"] == 1.0 for l in spec.layers)
+    zero = dict(CASES["a"], residual_mult=0.0)                       # nothing to fold: the block scales the sum
+    spec = _spec(zero)[2]
+    assert spec.layers[0].block_params["residual_mult"] == 0.0 and spec.embedding.params["scale"] == zero["embedding"]["scale"]
 
 
 @pytest.mark.parametrize("path,key", [((), "vocab"), ((), "residual_mult"), (("embedding",), "scale"), (("norm",), "eps"),

@@ -140,6 +140,23 @@ def test_a_new_prompt_beside_decoding_rows_and_a_long_decode(tmp_root, dtype):
     _check(torch.cat(got_b), torch.cat([wb[:1], wb[69:]]), dtype, "prompt beside decoding rows")
 
 
+def test_a_residual_factor_of_zero_and_of_one(tmp_root):
+    """Factors that cannot, or need not, be folded into the stream: 0 (the layers add nothing; the block scales the
+    sum itself) and 1."""
+    from tq_kv_b200.engine import StepRow
+    from rirudra_cases import make_weights
+    for m in (0.0, 1.0):
+        cfg = dict(CASES["a"], residual_mult=m)
+        path = pr.write_folder(os.path.join(str(tmp_root), f"factor_{m}"), cfg, make_weights(cfg, 2))
+        toks = tokens(70, cfg["vocab"], 3)
+        want = pr.decoder(cfg, pr.read_folder(path)[1], toks)
+        eng = _engine(path, "float32")
+        s = eng.new_sequence()
+        got = [eng.step([StepRow(s, toks[:60], list(range(60)))])]
+        got += [eng.step([StepRow(s, [t], [0])]) for t in toks[60:]]
+        _check(torch.cat(got), want, "float32", f"residual factor {m}")
+
+
 def _deciding_keys(path, toks):
     """For the one-layer sharp model: per position and head the key with the largest softmax weight, and that weight
     (from the plain implementation's own formulas)."""

@@ -347,3 +347,29 @@ def test_expanded_heads_for_prompts(dtype, H, d, r, e, n):
     y = torch.empty(T, H * e, dtype=dtype, device=DEV)
     kernels.latent_expand(vo, None, y, heads=H, kv_rank=hw, row_width=hw, value_dim=e, gate=gate)
     _close(y, wv[:, :, :e].reshape(T, -1) * torch.sigmoid(gate.double().cpu()), tol, "gated heads")
+
+
+@pytest.mark.parametrize("heads, width", [(32, 128), (24, 64), (17, 128), (6, 96)])
+def test_many_heads_on_one_shared_cache_row(heads, width):
+    """Decoded tokens whose heads all read ONE key/value head whose values are the keys themselves (the cache of a
+    latent), with more heads than one tensor-core tile holds: positions around page edges, one and several splits."""
+    from tq_kv_b200 import kernels
+    torch.manual_seed(heads)
+    pos_h = [0, 1, 63, 64, 65, 200, 399]
+    T = len(pos_h)
+    pages = torch.randn(T * 7, 1, 64, width, device=DEV).to(torch.bfloat16)
+    table = torch.randperm(T * 7, device=DEV).to(torch.int32).reshape(T, 7).contiguous()
+    q = (torch.randn(T, heads * width, device=DEV) * 0.5).to(torch.bfloat16)
+    want = torch.zeros(T, heads, width, dtype=torch.float64)
+    for t, p in enumerate(pos_h):
+        rows = torch.cat([pages[int(table[t, j]), 0] for j in range(p // 64 + 1)])[:p + 1].double().cpu()
+        s = q[t].double().cpu().reshape(heads, width) @ rows.T * 0.2
+        want[t] = torch.softmax(s, -1) @ rows
+    for n_splits in (1, 3):
+        out = torch.empty_like(q)
+        scratch = torch.empty(kernels.split_scratch_floats(T, heads, width, n_splits), device=DEV) if n_splits > 1 else None
+        kernels.attention(q, out, n_heads=heads, n_kv_heads=1, head_dim=width, tok_pos=_i32(pos_h),
+                          tok_seq=_i32(list(range(T))), cu_seqlens=_i32(list(range(T + 1))), start_pos=_i32(pos_h),
+                          window=None, scale=0.2, k_pages=pages, v_pages=pages, block_table=table, table_width=7,
+                          n_splits=n_splits, scratch=scratch)
+        _close(out, want.reshape(T, -1), 1.5e-2, f"{n_splits} splits")

@@ -239,8 +239,17 @@ def build_rirudra_spec(cfg: RirudraConfig) -> ModelSpec:
     """Rirudra as parts: scaled token embedding; per layer a parallel residual block of {RMS norm with weights
     stored around zero, the layer's mixer, and — unless the layer has none — SwiGLU}; the same norm once more;
     the embedding table as head."""
+    # A layer adds residual_mult * (its sublayers' results) to the stream x.  The stream is kept as x / residual_mult
+    # instead: the sublayers' results then enter it unscaled (in the epilogue of their last matrix products, with
+    # no kernel of their own), and since an RMS norm only sees its input's direction, norm(x) with eps equals the
+    # norm of the kept stream with eps / residual_mult^2.  Nothing else reads the stream.  (A factor of 0 cannot be
+    # folded; the block then scales the sum itself.)
+    m = cfg.residual_mult
+    fold = m not in (0.0, 1.0)
+    stream_eps = cfg.norm_eps / (m * m) if fold else cfg.norm_eps
+
     def norm(name: str) -> PartSpec:
-        return PartSpec("rms_norm", {"width": cfg.width, "eps": cfg.norm_eps, "weight_name": name, "weight_offset": 1.0})
+        return PartSpec("rms_norm", {"width": cfg.width, "eps": stream_eps, "weight_name": name, "weight_offset": 1.0})
 
     layers = []
     for i, layer in enumerate(cfg.layers):
@@ -252,14 +261,14 @@ def build_rirudra_spec(cfg: RirudraConfig) -> ModelSpec:
                                       "names": {"gate": "gate", "up": "up", "down": "down"}, "weight_suffix": ""},
                            p + "mlp.")
         layers.append(LayerSpec(block="parallel_residual", mixer=mixer, feed_forward=ffn, mixer_norm=norm(p + "norm1"),
-                                block_params={"residual_mult": cfg.residual_mult}))
+                                block_params={"residual_mult": 1.0 if fold else m}))
     spec = ModelSpec(
         architecture=ARCHITECTURE,
         vocab_size=cfg.vocab,
         hidden_size=cfg.width,
         max_positions=cfg.max_positions,
         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab, "width": cfg.width, "weight_name": "embed",
-                                               "scale": cfg.embedding_scale}),
+                                               "scale": cfg.embedding_scale / m if fold else cfg.embedding_scale}),
         layers=tuple(layers),
         schedule=tuple(ScheduleEntry(i) for i in range(len(layers))),
         final_norm=norm("final.norm"),

@@ -59,7 +59,9 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int window, float scale_log2,
                     bf16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int nh, int nkv,
                     int n_splits, const float* __restrict__ bias = nullptr, int n_dist = 0,
-                    const float* __restrict__ gate = nullptr, int ldg = 0) {
+                    const float* __restrict__ gate = nullptr, int ldg = 0, int kv_div = 1) {
+    // kv_div > 1: more than 16 q heads share a key/value head; they are cut into kv_div groups, each a block row of
+    // its own (nkv counts those groups), and group g reads the cache rows of head g / kv_div
     constexpr int ROW = HD * 2 + 16;                       // bytes per key row in shared memory (padded)
     constexpr int TILE = FD_CHUNK * ROW;                   // one K or V chunk
     constexpr int WARP_BYTES = FD_STAGES * 2 * TILE;
@@ -83,6 +85,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int n_chunks = hi > lo ? (hi - lo + FD_CHUNK - 1) / FD_CHUNK : 0;
     unsigned char* my = smem + warp * WARP_BYTES;
     const int* table = block_table + (size_t)b * table_width;
+    // a cache whose values are its keys (one row per token, read as both): the row is fetched once
+    const bool same_kv = (const void*)k_pages == (const void*)v_pages;
 
     // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < FD_CHUNK looks up the row
     // of key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte
@@ -95,7 +99,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             if (j >= hi) j = hi - 1;                       // a valid address; the score is masked
             int lp = j / FD_PAGE;
             if (ring_pages > 0) lp %= ring_pages;
-            const unsigned long long my_row = (((unsigned long long)table[lp] * nkv + g) * FD_PAGE + (j % FD_PAGE)) * HD;
+            const unsigned long long my_row =
+                (((unsigned long long)table[lp] * (nkv / kv_div) + g / kv_div) * FD_PAGE + (j % FD_PAGE)) * HD;
             unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
             unsigned char* vs_ = ks_ + TILE;
 #pragma unroll
@@ -104,7 +109,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 const int key = p / PR, c = p - key * PR;
                 const unsigned long long row = __shfl_sync(0xffffffffu, my_row, key);
                 fd_cp_async16(ks_ + key * ROW + c * 16, k_pages + row + c * 8);
-                fd_cp_async16(vs_ + key * ROW + c * 16, v_pages + row + c * 8);
+                if (!same_kv) fd_cp_async16(vs_ + key * ROW + c * 16, v_pages + row + c * 8);
             }
         }
         fd_commit();                                       // one group per turn, empty or not
@@ -152,7 +157,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         fd_wait<FD_STAGES - 1>();                          // chunk i has landed
         __syncwarp();
         const unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
-        const unsigned char* vs_ = ks_ + TILE;
+        const unsigned char* vs_ = same_kv ? ks_ : ks_ + TILE;
         const int j0 = lo + (warp + i * FD_WARPS) * FD_CHUNK;
 
         // S[16 heads x FD_CHUNK keys] = Q · K^T
@@ -318,7 +323,7 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
                                int ring_pages, const int* tok_pos, const int* tok_seq, int window, float scale,
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
                                int pdl_family, cudaStream_t stream, const float* bias = nullptr, int n_dist = 0,
-                               const float* gate = nullptr, int ldg = 0) {
+                               const float* gate = nullptr, int ldg = 0, int kv_div = 1) {
     constexpr int ROW = HD * 2 + 16;
     constexpr int FD_CHUNK = HD <= 64 ? 32 : 16;
     constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * 2 * FD_CHUNK * ROW;
@@ -337,12 +342,12 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
     const dim3 grid(n_tokens, nkv, n_splits);
     return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK, WEIGHTS>, grid, dim3(FD_WARPS * 32), smem, stream, q,
                          kp, vp, table, table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out,
-                         part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg);
+                         part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg, kv_div);
 }
 
 // Returns cudaErrorNotSupported (801) for shapes outside this kernel's reach
-// (head_dim not in {32, 64, 96, 128}, more than 16 q heads per key/value
-// head, pages of another size); the caller then uses the general kernel.
+// (head_dim not in {32, 64, 96, 128}, q heads per key/value head that do not
+// cut into equal groups of at most 16, pages of another size); the caller then uses the general kernel.
 //
 // `early_start`: launch the kernel so that it may begin while its predecessor in the stream still runs
 // (programmatic dependent launch).  Its blocks then read the positions, the block table and every key older than
@@ -355,15 +360,20 @@ static int flash_decode_launch(const void* q, const void* k_pages, const void* v
                                float* part_ml, int n_tokens, int nh, int nkv, int hd, int n_splits, int early_start,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || page_tokens != FD_PAGE || nkv > 65535 || n_splits > 65535)
-        return (int)cudaErrorNotSupported;
+    if (nkv <= 0 || nh % nkv || page_tokens != FD_PAGE) return (int)cudaErrorNotSupported;
+    // more than 16 q heads per key/value head: equal groups of at most 16, each a block row of its own
+    int kv_div = 1;
+    while (kv_div <= 64 && ((nh / nkv) % kv_div || nh / nkv / kv_div > 16)) ++kv_div;
+    if (kv_div > 64) return (int)cudaErrorNotSupported;
+    nkv *= kv_div;
+    if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorNotSupported;
     if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
 #define TQ_FD(H)                                                                                                  \
     case H:                                                                                                       \
         return launch_flash_decode<H>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table,   \
                                       table_width, ring_pages, tok_pos, tok_seq, window, scale, (bf16*)out,      \
                                       part_acc, part_ml, n_tokens, nh, nkv, n_splits,                \
-                                      early_start ? TQ_PDL_FLASH_DECODE : 0, stream)
+                                      early_start ? TQ_PDL_FLASH_DECODE : 0, stream, nullptr, 0, nullptr, 0, kv_div)
     switch (hd) {
         TQ_FD(32);
         TQ_FD(64);
