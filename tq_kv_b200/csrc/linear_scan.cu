@@ -129,6 +129,9 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
     constexpr int CT = THREADS / KG * RC;
     constexpr int NV = MODE == SCAN_DELTA ? 5 : 2;
     constexpr int SC = MODE >= SCAN_GATED ? 4 : 0;          // a token's scalars, in front of a stage
+    // tokens whose instructions the compiler may interleave (measured: the rules with one decay per head gain
+    // up to 10 % from four, 2,048 tokens of 16 heads of 128 x 128: 716 -> 643 us)
+    constexpr int TOKENS_AT_ONCE = MODE >= SCAN_GATED ? 4 : 2;
     extern __shared__ __align__(16) float sm[];
     const int b = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * CT;
     const int hq = head / a.qk_div;
@@ -232,7 +235,7 @@ __global__ void __launch_bounds__(THREADS) linear_scan_kernel(ScanArgs a) {
         const float* ssc = sm + s * stage_floats;
         const float* src = ssc + TC * SC;
         const float* sv = src + TC * NV * DP;
-#pragma unroll 2
+#pragma unroll TOKENS_AT_ONCE
         for (int tt = 0; tt < n; ++tt) {
             // Two neighbouring keys of one column share a 64-bit register pair, and the products run two at a
             // time (fma.rn.f32x2: each half is the IEEE fused multiply-add of the scalar instruction).

@@ -48,6 +48,7 @@ struct ConvArgs {
 
 __device__ __forceinline__ float conv_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+template <bool SINGLE>
 __global__ void __launch_bounds__(128) short_conv_kernel(ConvArgs a) {
     const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_wait();
@@ -86,17 +87,27 @@ __global__ void __launch_bounds__(128) short_conv_kernel(ConvArgs a) {
         vals[u] = 0.f;
         if (i < width) {
             const int c = c0 + i;
+            // four taps at a time: first their loads (which do not wait for one another), then the sums and,
+            // in a one-token step, the state's new rows (row j - 1 takes what row j held)
             float acc = a.bias ? a.bias[c] : 0.f;
-            float cur = 0.f;
-            for (int j = 0; j < K; ++j) {
-                const int idx = i_t - (K - 1) + j;           // input idx of this step (negative: from the state)
-                const float xin = idx >= 0 ? a.x[(size_t)(t0 + idx) * a.ldx + c] : st[(size_t)(K - 1 + idx) * C + c];
-                acc = fmaf(a.w[(size_t)c * K + j], xin, acc);
-                if (a.single && j > 0) {                     // one token: the state moves up by one row
-                    if (j < K - 1) st[(size_t)(j - 1) * C + c] = xin; else cur = xin;
+            for (int j0 = 0; j0 < K; j0 += 4) {
+                float xin[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int j = j0 + jj;
+                    const int idx = i_t - (K - 1) + j;       // input idx of this step (negative: from the state)
+                    xin[jj] = 0.f;
+                    if (j < K) xin[jj] = idx >= 0 ? a.x[(size_t)(t0 + idx) * a.ldx + c] : st[(size_t)(K - 1 + idx) * C + c];
+                }
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int j = j0 + jj;
+                    if (j < K) {
+                        acc = fmaf(a.w[(size_t)c * K + j], xin[jj], acc);
+                        if (SINGLE && j > 0) st[(size_t)(j - 1) * C + c] = xin[jj];
+                    }
                 }
             }
-            if (a.single && K > 1) st[(size_t)(K - 2) * C + c] = cur;
             if (a.silu) acc = acc / (1.f + expf(-acc));
             vals[u] = acc;
             ss = fmaf(acc, acc, ss);
@@ -175,7 +186,8 @@ TQ_API int tq_short_conv(const float* x, int ldx, const float* w, const float* b
     }
     const long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-    int st = tq_launch_pdl(TQ_PDL_ELEMENTWISE, short_conv_kernel, dim3((unsigned)blocks), dim3(128), 0, stream, a);
+    int st = single ? tq_launch_pdl(TQ_PDL_ELEMENTWISE, short_conv_kernel<true>, dim3((unsigned)blocks), dim3(128), 0, stream, a)
+                    : tq_launch_pdl(TQ_PDL_ELEMENTWISE, short_conv_kernel<false>, dim3((unsigned)blocks), dim3(128), 0, stream, a);
     if (st || single || K == 1) return st;
     const long long n = (long long)n_seqs * C;
     return tq_launch_pdl(TQ_PDL_ELEMENTWISE, short_conv_state_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
