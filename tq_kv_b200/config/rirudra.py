@@ -243,9 +243,9 @@ def build_rirudra_spec(cfg: RirudraConfig) -> ModelSpec:
     # instead: the sublayers' results then enter it unscaled (in the epilogue of their last matrix products, with
     # no kernel of their own), and since an RMS norm only sees its input's direction, norm(x) with eps equals the
     # norm of the kept stream with eps / residual_mult^2.  Nothing else reads the stream.  (A factor of 0 cannot be
-    # folded; the block then scales the sum itself.)
+    # folded, and a negative one would turn the norm's sign; the block then scales the sum itself.)
     m = cfg.residual_mult
-    fold = m not in (0.0, 1.0)
+    fold = m > 0.0 and m != 1.0
     stream_eps = cfg.norm_eps / (m * m) if fold else cfg.norm_eps
 
     def norm(name: str) -> PartSpec:
