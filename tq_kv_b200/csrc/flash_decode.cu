@@ -52,7 +52,10 @@ __device__ __forceinline__ uint32_t fd_pack(float a, float b) {
 #define FD_SIGMOID 1
 
 // FD_CHUNK: keys per warp iteration — 16, or 32 for heads of up to 64 dims, whose 16-key chunks would be too small.
-template <int HD, int FD_CHUNK, int WEIGHTS = FD_SOFTMAX>
+// VT: 1 if the values have a tile of their own beside the keys' in every stage; 0 for a cache whose values are its
+// keys (one row per token, given as both arrays): the row is fetched once and read as both operands, and the
+// shared memory that saves goes into longer chunks.
+template <int HD, int FD_CHUNK, int WEIGHTS = FD_SOFTMAX, int VT = 1>
 __global__ void __launch_bounds__(FD_WARPS * 32)
 flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     const int* __restrict__ block_table, int table_width, int ring_pages,
@@ -64,7 +67,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     // its own (nkv counts those groups), and group g reads the cache rows of head g / kv_div
     constexpr int ROW = HD * 2 + 16;                       // bytes per key row in shared memory (padded)
     constexpr int TILE = FD_CHUNK * ROW;                   // one K or V chunk
-    constexpr int WARP_BYTES = FD_STAGES * 2 * TILE;
+    constexpr int TPS = VT ? 2 : 1;                        // tiles per stage
+    constexpr int WARP_BYTES = FD_STAGES * TPS * TILE;
     constexpr int KS = HD / 16;                            // k-steps of Q·K^T
     constexpr int NT = HD / 8;                             // n-tiles of P·V
     extern __shared__ __align__(16) unsigned char smem[];
@@ -85,8 +89,6 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int n_chunks = hi > lo ? (hi - lo + FD_CHUNK - 1) / FD_CHUNK : 0;
     unsigned char* my = smem + warp * WARP_BYTES;
     const int* table = block_table + (size_t)b * table_width;
-    // a cache whose values are its keys (one row per token, read as both): the row is fetched once
-    const bool same_kv = (const void*)k_pages == (const void*)v_pages;
 
     // issue the copy of this warp's i-th chunk into stage i % FD_STAGES.  Lane l < FD_CHUNK looks up the row
     // of key l; then consecutive lanes copy consecutive 16-byte pieces of a row, so that every 32-byte
@@ -101,7 +103,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             if (ring_pages > 0) lp %= ring_pages;
             const unsigned long long my_row =
                 (((unsigned long long)table[lp] * (nkv / kv_div) + g / kv_div) * FD_PAGE + (j % FD_PAGE)) * HD;
-            unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
+            unsigned char* ks_ = my + (i % FD_STAGES) * TPS * TILE;
             unsigned char* vs_ = ks_ + TILE;
 #pragma unroll
             for (int it = 0; it < FD_CHUNK * PR / 32; ++it) {
@@ -109,7 +111,7 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 const int key = p / PR, c = p - key * PR;
                 const unsigned long long row = __shfl_sync(0xffffffffu, my_row, key);
                 fd_cp_async16(ks_ + key * ROW + c * 16, k_pages + row + c * 8);
-                if (!same_kv) fd_cp_async16(vs_ + key * ROW + c * 16, v_pages + row + c * 8);
+                if (VT) fd_cp_async16(vs_ + key * ROW + c * 16, v_pages + row + c * 8);
             }
         }
         fd_commit();                                       // one group per turn, empty or not
@@ -156,8 +158,8 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         issue(i + FD_STAGES - 1);
         fd_wait<FD_STAGES - 1>();                          // chunk i has landed
         __syncwarp();
-        const unsigned char* ks_ = my + (i % FD_STAGES) * 2 * TILE;
-        const unsigned char* vs_ = same_kv ? ks_ : ks_ + TILE;
+        const unsigned char* ks_ = my + (i % FD_STAGES) * TPS * TILE;
+        const unsigned char* vs_ = VT ? ks_ + TILE : ks_;
         const int j0 = lo + (warp + i * FD_WARPS) * FD_CHUNK;
 
         // S[16 heads x FD_CHUNK keys] = Q · K^T
@@ -318,15 +320,15 @@ flash_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     }
 }
 
-template <int HD, int WEIGHTS = FD_SOFTMAX>
+template <int HD, int WEIGHTS = FD_SOFTMAX, int VT = 1>
 static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, const int* table, int table_width,
                                int ring_pages, const int* tok_pos, const int* tok_seq, int window, float scale,
                                bf16* out, float* part_acc, float* part_ml, int n_tokens, int nh, int nkv, int n_splits,
                                int pdl_family, cudaStream_t stream, const float* bias = nullptr, int n_dist = 0,
                                const float* gate = nullptr, int ldg = 0, int kv_div = 1) {
     constexpr int ROW = HD * 2 + 16;
-    constexpr int FD_CHUNK = HD <= 64 ? 32 : 16;
-    constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * 2 * FD_CHUNK * ROW;
+    constexpr int FD_CHUNK = (HD <= 64 || !VT) ? 32 : 16;
+    constexpr size_t stage_bytes = (size_t)FD_WARPS * FD_STAGES * (VT ? 2 : 1) * FD_CHUNK * ROW;
     constexpr size_t merge_bytes = (size_t)FD_WARPS * 16 * (HD + 2) * sizeof(float);
     constexpr size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured[64] = {false};         // per device: the attribute belongs to the device's copy of the kernel
@@ -334,13 +336,13 @@ static int launch_flash_decode(const bf16* q, const bf16* kp, const bf16* vp, co
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK, WEIGHTS>,
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<HD, FD_CHUNK, WEIGHTS, VT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
     const dim3 grid(n_tokens, nkv, n_splits);
-    return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK, WEIGHTS>, grid, dim3(FD_WARPS * 32), smem, stream, q,
+    return tq_launch_pdl(pdl_family, flash_decode_kernel<HD, FD_CHUNK, WEIGHTS, VT>, grid, dim3(FD_WARPS * 32), smem, stream, q,
                          kp, vp, table, table_width, ring_pages, tok_pos, tok_seq, window, scale * 1.4426950408889634f, out,
                          part_acc, part_ml, nh, nkv, n_splits, bias, n_dist, gate, ldg, kv_div);
 }
@@ -368,12 +370,13 @@ static int flash_decode_launch(const void* q, const void* k_pages, const void* v
     nkv *= kv_div;
     if (nkv > 65535 || n_splits > 65535) return (int)cudaErrorNotSupported;
     if (n_splits < 1 || (n_splits > 1 && (!part_acc || !part_ml))) return (int)cudaErrorInvalidValue;
+    const bool same = k_pages == v_pages;               // the values are the keys: one tile per stage
+#define TQ_FD_ARGS (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_width, ring_pages,      \
+                   tok_pos, tok_seq, window, scale, (bf16*)out, part_acc, part_ml, n_tokens, nh, nkv, n_splits,            \
+                   early_start ? TQ_PDL_FLASH_DECODE : 0, stream, nullptr, 0, nullptr, 0, kv_div
 #define TQ_FD(H)                                                                                                  \
     case H:                                                                                                       \
-        return launch_flash_decode<H>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table,   \
-                                      table_width, ring_pages, tok_pos, tok_seq, window, scale, (bf16*)out,      \
-                                      part_acc, part_ml, n_tokens, nh, nkv, n_splits,                \
-                                      early_start ? TQ_PDL_FLASH_DECODE : 0, stream, nullptr, 0, nullptr, 0, kv_div)
+        return same ? launch_flash_decode<H, FD_SOFTMAX, 0>(TQ_FD_ARGS) : launch_flash_decode<H, FD_SOFTMAX, 1>(TQ_FD_ARGS)
     switch (hd) {
         TQ_FD(32);
         TQ_FD(64);
@@ -381,6 +384,7 @@ static int flash_decode_launch(const void* q, const void* k_pages, const void* v
         TQ_FD(128);
         default: return (int)cudaErrorNotSupported;
     }
+#undef TQ_FD_ARGS
 #undef TQ_FD
 }
 
